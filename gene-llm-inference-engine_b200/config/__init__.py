@@ -2,9 +2,10 @@ from .base import ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .llama import LlamaConfig, RopeScaling, parse_rope_scaling
 from .nipadra import NipadraConfig
 from .gekupel import GekupelConfig
+from .pinorax import PinoraxConfig
 from .registry import (Architecture, known_architectures, parse_config, register_architecture,
                        resolve_architecture)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "LlamaConfig", "NipadraConfig", "GekupelConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "LlamaConfig", "NipadraConfig", "GekupelConfig", "PinoraxConfig",
            "RopeScaling", "parse_rope_scaling", "Architecture", "known_architectures", "parse_config",
            "register_architecture", "resolve_architecture"]

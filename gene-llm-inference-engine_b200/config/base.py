@@ -67,6 +67,8 @@ class ModelSpec:
     final_norm: PartSpec
     tie_word_embeddings: bool
     embedding_scale: float = 1.0   # multiplier on embedding rows (1 = none)
+    # what is added to the embedding's output per position (kind "learned": a table of vectors); None = nothing
+    embedding_position: Optional[PartSpec] = None
     logit_transform: Optional[PartSpec] = None   # applied to the logits after the head (a scale, a soft cap); None = none
     # a design without a context length of its own: ``max_position`` is then only the engine's default, and the
     # caller's limit may exceed it

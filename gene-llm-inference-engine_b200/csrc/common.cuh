@@ -105,6 +105,20 @@ __device__ __forceinline__ float att_finish(const AttEpilogue& e, float l, float
     return f;
 }
 
+// act(gate) * up of a gated feed-forward, 32-bit. 0 SiLU, 1 ReLU, 2 tanh-GELU; 3 ("capped swish"): the gate is capped from
+// above at `limit`, the up value clamped to [-limit, limit], and the result is gate * sigmoid(1.702 gate) * (up + 1).
+enum GateAct : int { kActSilu = 0, kActRelu = 1, kActGeluTanh = 2, kActCappedSwish = 3, kActCount = 4 };
+__device__ __forceinline__ float gated_value(float g, float u, int act, float limit) {
+    if (act == kActRelu) return fmaxf(g, 0.f) * u;
+    if (act == kActGeluTanh) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    if (act == kActCappedSwish) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+    }
+    return g * (1.0f / (1.0f + expf(-g))) * u;
+}
+
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};

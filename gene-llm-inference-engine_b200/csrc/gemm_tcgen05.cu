@@ -927,7 +927,9 @@ struct TcPersistentParams {
     int rows_p, rows_q, K;       // tokens, output columns of the accumulator tile space, reduction length
     int tiles_p, tiles_q;
     int up_row_offset;           // SwiGLU: row of the first up channel in the weight (= I)
-    int gate_act;                // SwiGLU epilogue: what is applied to the gate (0 SiLU, 1 ReLU, 2 tanh-GELU)
+    int gate_act;                // SwiGLU epilogue: what is applied to the gate (a GateAct code)
+    float act_limit;             //   its limit (capped swish)
+    const float* gate_up_bias;   //   optional: a bias on the gate channels and, up_row_offset values further, on the up channels
     int* status;
     int splits;                  // K is cut into this many ranges, each an accumulator tile of its own whose result is
     int kb_per_split;            //   stored split_rows rows further down in the output (a workspace; the ranges are
@@ -1253,17 +1255,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                             for (int e = 0; e < 4; ++e) {
                                 const float g0 = __uint_as_float(r[q4 * 8 + 2 * e]), g1 = __uint_as_float(r[q4 * 8 + 2 * e + 1]);
                                 const float u0 = __uint_as_float(u[q4 * 8 + 2 * e]), u1 = __uint_as_float(u[q4 * 8 + 2 * e + 1]);
-                                float h0, h1;
-                                if (p.gate_act == 0) {
-                                    h0 = g0 * (1.0f / (1.0f + expf(-g0))) * u0;
-                                    h1 = g1 * (1.0f / (1.0f + expf(-g1))) * u1;
-                                } else if (p.gate_act == 1) {
-                                    h0 = fmaxf(g0, 0.f) * u0;
-                                    h1 = fmaxf(g1, 0.f) * u1;
-                                } else {
-                                    h0 = 0.5f * g0 * (1.0f + tanhf(0.7978845608028654f * (g0 + 0.044715f * g0 * g0 * g0))) * u0;
-                                    h1 = 0.5f * g1 * (1.0f + tanhf(0.7978845608028654f * (g1 + 0.044715f * g1 * g1 * g1))) * u1;
+                                float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
+                                if (p.gate_up_bias) {             // a bias per gate and up channel (gate values first)
+                                    const int gc = tile_q * (BLOCK_Q / 2) + ch + q4 * 8 + 2 * e;
+                                    if (gc < p.rows_q) { b0 = __ldg(p.gate_up_bias + gc); c0 = __ldg(p.gate_up_bias + p.up_row_offset + gc); }
+                                    if (gc + 1 < p.rows_q) { b1 = __ldg(p.gate_up_bias + gc + 1); c1 = __ldg(p.gate_up_bias + p.up_row_offset + gc + 1); }
                                 }
+                                const float h0 = gated_value(g0 + b0, u0 + c0, p.gate_act, p.act_limit);
+                                const float h1 = gated_value(g1 + b1, u1 + c1, p.gate_act, p.act_limit);
                                 __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
                                 packed[e] = *reinterpret_cast<uint32_t*>(&hb);
                             }
@@ -1722,15 +1721,17 @@ __global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __rest
 // pair: the product runs on pairs of CTAs that share 256-row tiles of tokens (block_q 256 only).
 static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int epilogue, int M, int N, int K,
                                      long long lda, long long ldw, long long ldc, int block_q, void* status,
-                                     int splits, void* workspace, long long workspace_floats, int pair, void* stream) {
+                                     int splits, void* workspace, long long workspace_floats, int pair, float act_limit,
+                                     const float* gate_up_bias, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tc: K=%d and the row strides (%lld, %lld) must be multiples of 8 (16-byte rows for TMA)", K, lda, ldw);
     const int gate_act = epilogue >> 8;
     epilogue &= 0xff;
-    GI_REQUIRE(epilogue >= 0 && epilogue <= 2 && gate_act >= 0 && gate_act <= 2 && (gate_act == 0 || epilogue == kEpiSwiGLU),
+    GI_REQUIRE(epilogue >= 0 && epilogue <= 2 && gate_act >= 0 && gate_act < kActCount && (gate_act == 0 || epilogue == kEpiSwiGLU),
                "gemm_tc: unknown epilogue %d (activation %d)", epilogue, gate_act);
+    GI_REQUIRE(gate_up_bias == nullptr || epilogue == kEpiSwiGLU, "gemm_tc: a gate/up bias goes with the gated epilogue only");
     const bool bf16_out = epilogue == kEpiSwiGLU;
     GI_REQUIRE((ldc * (bf16_out ? 2 : 4)) % 16 == 0, "gemm_tc: the output row stride %lld is not a multiple of 16 bytes", ldc);
     GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0) &&
@@ -1743,7 +1744,7 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     p.tiles_p = pair ? (M + 2 * kBlockP - 1) / (2 * kBlockP) : (M + kBlockP - 1) / kBlockP;
     const int rows_per_tile_p = pair ? 2 * kBlockP : kBlockP;
     p.up_row_offset = N;
-    p.gate_act = gate_act;
+    p.gate_act = gate_act; p.act_limit = act_limit; p.gate_up_bias = gate_up_bias;
     p.status = static_cast<int*>(status);
     const int total_kb = (K + kBlockK - 1) / kBlockK;
     p.splits = 1; p.kb_per_split = total_kb; p.split_rows = 0;
@@ -1798,14 +1799,14 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
 // with epilogue 2), tile_group[i] the group of tile i and *tiles_used how many tiles exist (device memory, written by
 // an earlier kernel). C [M, N] in the rows' order; epilogue 0 stores 32-bit, 2 stores act(gate) * up as bfloat16.
 static int gi_gemm_tc_grouped_impl(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, int groups,
-                                  const int* tile_group, const int* tiles_used, void* status, void* stream) {
+                                  const int* tile_group, const int* tiles_used, void* status, float act_limit, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0, "gemm_tc grouped: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(M % kBlockP == 0, "gemm_tc grouped: %d rows are not whole tiles of %d", M, kBlockP);
     GI_REQUIRE(K % 8 == 0, "gemm_tc grouped: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
     const int gate_act = epilogue >> 8;
     epilogue &= 0xff;
-    GI_REQUIRE((epilogue == kEpiStoreF32 || epilogue == kEpiSwiGLU) && gate_act >= 0 && gate_act <= 2,
+    GI_REQUIRE((epilogue == kEpiStoreF32 || epilogue == kEpiSwiGLU) && gate_act >= 0 && gate_act < kActCount,
                "gemm_tc grouped: unknown epilogue %d (activation %d)", epilogue, gate_act);
     const bool bf16_out = epilogue == kEpiSwiGLU;
     GI_REQUIRE((static_cast<long long>(N) * (bf16_out ? 2 : 4)) % 16 == 0, "gemm_tc grouped: output rows of %d values are not a multiple of 16 bytes", N);
@@ -1817,7 +1818,7 @@ static int gi_gemm_tc_grouped_impl(const void* A, const void* W, void* C, int ep
     p.rows_p = M; p.rows_q = N; p.K = K;
     p.tiles_p = M / kBlockP;
     p.up_row_offset = N;
-    p.gate_act = gate_act;
+    p.gate_act = gate_act; p.act_limit = act_limit; p.gate_up_bias = nullptr;
     p.status = static_cast<int*>(status);
     p.splits = 1; p.kb_per_split = (K + kBlockK - 1) / kBlockK; p.split_rows = 0;
     p.tile_group = tile_group; p.tiles_used = tiles_used; p.group_rows = bf16_out ? 2 * N : N;
@@ -1902,12 +1903,12 @@ extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long 
     return gi::dispatch(gi_gemm_tc_rope_impl, A, W, M, K, lda, ldw, block_q, splits, workspace, workspace_floats, counters, n_counters, status, w_tiles, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, H, Hkv, hd, page_size, write_kv, stream);
 }
 
-extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, long long lda, long long ldw, long long ldc, int block_q, void* status, int splits, void* workspace, long long workspace_floats, int pair, void* stream) {
-    return gi::dispatch(gi_gemm_tc_persistent_impl, A, W, C, epilogue, M, N, K, lda, ldw, ldc, block_q, status, splits, workspace, workspace_floats, pair, stream);
+extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, long long lda, long long ldw, long long ldc, int block_q, void* status, int splits, void* workspace, long long workspace_floats, int pair, float act_limit, const float* gate_up_bias, void* stream) {
+    return gi::dispatch(gi_gemm_tc_persistent_impl, A, W, C, epilogue, M, N, K, lda, ldw, ldc, block_q, status, splits, workspace, workspace_floats, pair, act_limit, gate_up_bias, stream);
 }
 
-extern "C" int gi_gemm_tc_grouped(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, int groups, const int* tile_group, const int* tiles_used, void* status, void* stream) {
-    return gi::dispatch(gi_gemm_tc_grouped_impl, A, W, C, epilogue, M, N, K, groups, tile_group, tiles_used, status, stream);
+extern "C" int gi_gemm_tc_grouped(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, int groups, const int* tile_group, const int* tiles_used, void* status, float act_limit, void* stream) {
+    return gi::dispatch(gi_gemm_tc_grouped_impl, A, W, C, epilogue, M, N, K, groups, tile_group, tiles_used, status, act_limit, stream);
 }
 
 extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* status, int pair, void* stream) {

@@ -33,16 +33,10 @@ struct GroupedArgs {
     void* out; int out_is_f32; long long ldo; int o_off; int o_gs;
     int N, K, rows, groups;
     const int* tile_group; const int* sorted_rows; const int* n_tiles;   // experts form (else null)
-    int act;                                                      // gated: 0 SiLU, 1 ReLU, 2 tanh-GELU
+    int act; float act_limit;                                     // gated: a GateAct code and its limit
     // rotated tail (heads form)
     int tail; const float* freq; float amplitude; const int* positions;
 };
-
-__device__ __forceinline__ float gp_act(float g, int act) {
-    if (act == 1) return fmaxf(g, 0.f);
-    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-    return g * (1.0f / (1.0f + expf(-g)));
-}
 
 template <typename TA, typename TW, bool GATED>
 __global__ void __launch_bounds__(128)
@@ -135,7 +129,7 @@ grouped_product_kernel(const GroupedArgs p) {
             const int n = n0 + tn + j;
             if (n >= p.N) continue;
             float v = acc[i][j];
-            if (GATED) v = gp_act(v, p.act) * acc_up[U * i][j];
+            if (GATED) v = gated_value(v, acc_up[U * i][j], p.act, p.act_limit);
             const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
             if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
             else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
@@ -254,7 +248,7 @@ grouped_rows_kernel(const GroupedArgs p) {
             for (int i = 0; i < kGrFew; ++i) {
                 if (i < m_here && n_first + r < p.N) {
                     float v = warp_sum(acc[r][i]);
-                    if (GATED) v = gp_act(v, p.act) * warp_sum(acc_up[GATED ? r : 0][i]);
+                    if (GATED) v = gated_value(v, warp_sum(acc_up[GATED ? r : 0][i]), p.act, p.act_limit);
                     if (lane == 0) {
                         const size_t o = static_cast<size_t>(s_row[m0 + i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n_first + r;
                         if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
@@ -397,6 +391,23 @@ route_kernel(const TX* __restrict__ x, int D, const float* __restrict__ w, const
     }
 }
 
+// Experts fixed per token id: ids[t, :] = table[token of row t, :], every weight 1 / top. A token given as -(k + 1) is read
+// from place k of the feedback buffer (the id a sampling kernel left on the device), as the embedding kernel reads it.
+__global__ void __launch_bounds__(256)
+route_table_kernel(const int* __restrict__ tokens, const int* __restrict__ feedback, const int* __restrict__ table, int vocab, int E,
+                   int top, int* __restrict__ ids, float* __restrict__ weights, int n_pairs) {
+    pdl_prologue();
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_pairs) return;
+    int tok = tokens[i / top];
+    if (tok < 0) tok = feedback ? feedback[-tok - 1] : 0;
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    int e = table[static_cast<size_t>(tok) * top + i % top];
+    e = e < 0 ? 0 : (e >= E ? E - 1 : e);                  // the table is checked when the model is built
+    ids[i] = e;
+    weights[i] = 1.0f / static_cast<float>(top);
+}
+
 // One block: counts per expert, then tiles of 16 rows per expert in expert order.
 __global__ void __launch_bounds__(1024)
 route_align_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ sorted_rows, int* __restrict__ tile_group,
@@ -536,19 +547,19 @@ static int gi_head_product_impl(const void* a, int a_dtype, long long lda, int a
 }
 
 static int gi_expert_product_impl(const void* a, int a_dtype, long long lda, int a_div, const void* w, int w_dtype, long long w_gs,
-                                  int ldw, long long up_off, int gated, int act, void* out, int out_dtype, long long ldo,
+                                  int ldw, long long up_off, int gated, int act, float act_limit, void* out, int out_dtype, long long ldo,
                                   int N, int K, const int* tile_group, const int* sorted_rows, const int* n_tiles, int max_tiles,
                                   void* stream) {
     if (max_tiles == 0) return 0;
     GI_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && a_div > 0, "expert_product: sizes must be positive");
     GI_REQUIRE(tile_group && sorted_rows && n_tiles, "expert_product: the sorted rows are missing");
-    GI_REQUIRE(act >= 0 && act <= 2, "expert_product: unknown activation code %d", act);
+    GI_REQUIRE(act >= 0 && act < kActCount, "expert_product: unknown activation code %d", act);
     GroupedArgs p = {};
     p.a = a; p.lda = lda; p.a_div = a_div;
     p.w = w; p.w_gs = w_gs; p.ldw = ldw; p.up_off = up_off;
     p.out = out; p.out_is_f32 = out_dtype == kF32; p.ldo = ldo;
     p.N = N; p.K = K; p.groups = 1;
-    p.tile_group = tile_group; p.sorted_rows = sorted_rows; p.n_tiles = n_tiles; p.act = act;
+    p.tile_group = tile_group; p.sorted_rows = sorted_rows; p.n_tiles = n_tiles; p.act = act; p.act_limit = act_limit;
     dim3 grid(max_tiles, (N + kGpTN - 1) / kGpTN);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows_form_fits(p, a_dtype, w_dtype))
@@ -578,6 +589,23 @@ static int gi_route_impl(const void* x, int x_dtype, int T, int D, const float* 
         GI_REQUIRE(false, "route: unsupported dtype code %d", x_dtype);
     }
     if (check_launch("route")) return 1;
+    launch_kernel(route_align_kernel, dim3(1), dim3(1024), 0, st, static_cast<const int*>(ids), static_cast<int>(pairs), E, sorted_rows, tile_group, n_tiles, max_tiles, tile_rows, pair_row);
+    return check_launch("route_align");
+}
+
+static int gi_route_table_impl(const int* tokens, const int* feedback, const int* table, int vocab, int T, int E, int top, int* ids,
+                               float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, int tile_rows,
+                               int* pair_row, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && vocab > 0 && E > 0 && top > 0 && top <= E, "route_table: sizes must be positive and top at most the experts");
+    GI_REQUIRE(E <= kRouteMaxExperts, "route_table: %d experts exceed %d", E, kRouteMaxExperts);
+    const long long pairs = static_cast<long long>(T) * top;
+    GI_REQUIRE(tile_rows > 0 && pairs <= 2147483647LL, "route_table: tiles must have rows");
+    GI_REQUIRE(max_tiles >= (pairs + tile_rows - 1) / tile_rows + std::min<long long>(E, pairs) - 1, "route_table: room for %d tiles is too little", max_tiles);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    launch_kernel(route_table_kernel, dim3(static_cast<unsigned>((pairs + 255) / 256)), dim3(256), 0, st, tokens, feedback, table, vocab, E, top,
+                  ids, weights, static_cast<int>(pairs));
+    if (check_launch("route_table")) return 1;
     launch_kernel(route_align_kernel, dim3(1), dim3(1024), 0, st, static_cast<const int*>(ids), static_cast<int>(pairs), E, sorted_rows, tile_group, n_tiles, max_tiles, tile_rows, pair_row);
     return check_launch("route_align");
 }
@@ -615,9 +643,9 @@ extern "C" int gi_head_product(const void* a, int a_dtype, long long lda, int a_
 }
 
 extern "C" int gi_expert_product(const void* a, int a_dtype, long long lda, int a_div, const void* w, int w_dtype, long long w_gs,
-                                 int ldw, long long up_off, int gated, int act, void* out, int out_dtype, long long ldo, int N, int K,
+                                 int ldw, long long up_off, int gated, int act, float act_limit, void* out, int out_dtype, long long ldo, int N, int K,
                                  const int* tile_group, const int* sorted_rows, const int* n_tiles, int max_tiles, void* stream) {
-    return gi::dispatch(gi_expert_product_impl, a, a_dtype, lda, a_div, w, w_dtype, w_gs, ldw, up_off, gated, act, out, out_dtype, ldo,
+    return gi::dispatch(gi_expert_product_impl, a, a_dtype, lda, a_div, w, w_dtype, w_gs, ldw, up_off, gated, act, act_limit, out, out_dtype, ldo,
                         N, K, tile_group, sorted_rows, n_tiles, max_tiles, stream);
 }
 
@@ -625,6 +653,13 @@ extern "C" int gi_route(const void* x, int x_dtype, int T, int D, const float* w
                         float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, int tile_rows, int* pair_row,
                         void* stream) {
     return gi::dispatch(gi_route_impl, x, x_dtype, T, D, w, correction, E, top, ids, weights, sorted_rows, tile_group, n_tiles,
+                        max_tiles, tile_rows, pair_row, stream);
+}
+
+extern "C" int gi_route_table(const int* tokens, const int* feedback, const int* table, int vocab, int T, int E, int top, int* ids,
+                              float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, int tile_rows,
+                              int* pair_row, void* stream) {
+    return gi::dispatch(gi_route_table_impl, tokens, feedback, table, vocab, T, E, top, ids, weights, sorted_rows, tile_group, n_tiles,
                         max_tiles, tile_rows, pair_row, stream);
 }
 

@@ -5,7 +5,7 @@
 //                   reads (xn) and what it adds its output to (acc)
 //   residual_norm   x = w * (acc / sqrt(mean(acc^2) + eps)) in 32-bit, in one pass also the next sublayer's
 //                   xn = x (compute dtype) and acc = alpha * x
-//   gated_act       out = act(gate) * up for act in {SiLU, ReLU, tanh-GELU}
+//   gated_act       out = act(gate) * up for act in {SiLU, ReLU, tanh-GELU, capped swish}, optionally with a bias on both
 //   norm_rope_store per token and head: optional unit-RMS norm with a weight shared by all heads, rotation of the
 //                   first 2 * rot_half dimensions by angles position * freq[i] computed here in 32-bit (no table
 //                   of max_position rows), queries to q_out, keys to the token's page row; the values stored beside
@@ -68,36 +68,39 @@ residual_norm_kernel(const float* __restrict__ acc_in, const float* __restrict__
     }
 }
 
-__device__ __forceinline__ float act_apply(float g, int act) {
-    if (act == 1) return fmaxf(g, 0.f);
-    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-    return g * (1.0f / (1.0f + expf(-g)));
-}
-
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-gated_act_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I, size_t total, int act) {
+gated_act_kernel(const float* __restrict__ gu, const float* __restrict__ bias, TOut* __restrict__ out, int I, size_t total, int act,
+                 float limit) {
     pdl_prologue();
     const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / I;
     const int c = static_cast<int>(i % I);
-    out[i] = from_float<TOut>(act_apply(gu[t * 2 * I + c], act) * gu[t * 2 * I + I + c]);
+    float g = gu[t * 2 * I + c], u = gu[t * 2 * I + I + c];
+    if (bias) { g += bias[c]; u += bias[I + c]; }
+    out[i] = from_float<TOut>(gated_value(g, u, act, limit));
 }
 
 // The same, four channels to a thread with 16-byte accesses (I a multiple of 4, pointers aligned).
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-gated_act4_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I4, size_t total4, int act) {
+gated_act4_kernel(const float* __restrict__ gu, const float* __restrict__ bias, TOut* __restrict__ out, int I4, size_t total4, int act,
+                  float limit) {
     pdl_prologue();
     const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total4) return;
     const size_t t = i / I4;
     const int c = static_cast<int>(i % I4);
     const float4* row = reinterpret_cast<const float4*>(gu) + t * 2 * I4;
-    const float4 g = row[c], u = row[I4 + c];
-    const float r0 = act_apply(g.x, act) * u.x, r1 = act_apply(g.y, act) * u.y, r2 = act_apply(g.z, act) * u.z,
-                r3 = act_apply(g.w, act) * u.w;
+    float4 g = row[c], u = row[I4 + c];
+    if (bias) {
+        const float4 bg = reinterpret_cast<const float4*>(bias)[c], bu = reinterpret_cast<const float4*>(bias)[I4 + c];
+        g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w;
+        u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
+    }
+    const float r0 = gated_value(g.x, u.x, act, limit), r1 = gated_value(g.y, u.y, act, limit), r2 = gated_value(g.z, u.z, act, limit),
+                r3 = gated_value(g.w, u.w, act, limit);
     if constexpr (sizeof(TOut) == 4) {
         *reinterpret_cast<float4*>(out + 4 * i) = make_float4(r0, r1, r2, r3);
     } else {
@@ -289,26 +292,26 @@ static int gi_residual_norm_impl(const float* acc_in, const float* weight, float
     return check_launch("residual_norm");
 }
 
-static int gi_gated_act_impl(const float* gate_up, void* out, int out_dtype, int T, int I, int act, void* stream) {
+static int gi_gated_act_impl(const float* gate_up, const float* bias, void* out, int out_dtype, int T, int I, int act, float limit, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && I > 0, "gated_act: sizes must be positive (T=%d, I=%d)", T, I);
-    GI_REQUIRE(act >= 0 && act <= 2, "gated_act: unknown activation code %d", act);
+    GI_REQUIRE(act >= 0 && act < kActCount, "gated_act: unknown activation code %d", act);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t total = static_cast<size_t>(T) * I;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
     if (I % 4 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
-        (out_dtype == kBF16 || out_dtype == kF32)) {
+        reinterpret_cast<uintptr_t>(bias) % 16 == 0 && (out_dtype == kBF16 || out_dtype == kF32)) {
         const unsigned blocks4 = static_cast<unsigned>((total / 4 + 255) / 256);
         if (out_dtype == kBF16)
-            launch_kernel((gated_act4_kernel<__nv_bfloat16>), dim3(blocks4), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I / 4, total / 4, act);
+            launch_kernel((gated_act4_kernel<__nv_bfloat16>), dim3(blocks4), dim3(256), 0, st, gate_up, bias, static_cast<__nv_bfloat16*>(out), I / 4, total / 4, act, limit);
         else
-            launch_kernel((gated_act4_kernel<float>), dim3(blocks4), dim3(256), 0, st, gate_up, static_cast<float*>(out), I / 4, total / 4, act);
+            launch_kernel((gated_act4_kernel<float>), dim3(blocks4), dim3(256), 0, st, gate_up, bias, static_cast<float*>(out), I / 4, total / 4, act, limit);
         return check_launch("gated_act");
     }
     if (out_dtype == kBF16)
-        launch_kernel((gated_act_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I, total, act);
+        launch_kernel((gated_act_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, bias, static_cast<__nv_bfloat16*>(out), I, total, act, limit);
     else if (out_dtype == kF32)
-        launch_kernel((gated_act_kernel<float>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<float*>(out), I, total, act);
+        launch_kernel((gated_act_kernel<float>), dim3(blocks), dim3(256), 0, st, gate_up, bias, static_cast<float*>(out), I, total, act, limit);
     else
         GI_REQUIRE(false, "gated_act: unsupported output dtype code %d", out_dtype);
     return check_launch("gated_act");
@@ -353,8 +356,8 @@ extern "C" int gi_residual_norm(const float* acc_in, const float* weight, float*
     return gi::dispatch(gi_residual_norm_impl, acc_in, weight, x_out, acc_out, xn_out, xn_dtype, rows, D, eps, alpha, stream);
 }
 
-extern "C" int gi_gated_act(const float* gate_up, void* out, int out_dtype, int T, int I, int act, void* stream) {
-    return gi::dispatch(gi_gated_act_impl, gate_up, out, out_dtype, T, I, act, stream);
+extern "C" int gi_gated_act(const float* gate_up, const float* bias, void* out, int out_dtype, int T, int I, int act, float limit, void* stream) {
+    return gi::dispatch(gi_gated_act_impl, gate_up, bias, out, out_dtype, T, I, act, limit, stream);
 }
 
 extern "C" int gi_norm_rope_store(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_half, int interleaved, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int vd, int page_size, int write_kv, void* stream) {

@@ -188,7 +188,9 @@ def rope_store(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor
         "rope_store")
 
 
-ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+# what a gated feed-forward applies to (gate, up): act(gate) * up, except "capped_swish" (with ``limit`` L):
+# g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1)
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "capped_swish": 3}
 
 
 def scale_cast(x: torch.Tensor, acc: torch.Tensor, xn: Optional[torch.Tensor], alpha: float) -> None:
@@ -217,15 +219,17 @@ def residual_norm(acc: torch.Tensor, weight: torch.Tensor, x_out: torch.Tensor, 
                                  _stream()), "residual_norm")
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """out = act(gate_up[:, :I]) * gate_up[:, I:] for act in ACTIVATIONS."""
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0,
+              bias: Optional[torch.Tensor] = None) -> None:
+    """out = act(gate_up[:, :I]) * gate_up[:, I:] for act in ACTIVATIONS (``limit``: the bound of "capped_swish");
+    ``bias`` [2I] 32-bit is added to gate_up first."""
     T, I = out.shape
-    if gate_up.shape != (T, 2 * I):
-        raise KernelError("gated_act: gate_up must be [T, 2I] for out [T, I]")
+    if gate_up.shape != (T, 2 * I) or (bias is not None and bias.numel() != 2 * I):
+        raise KernelError("gated_act: gate_up must be [T, 2I] for out [T, I] (and the bias [2I])")
     if activation not in ACTIVATIONS:
         raise KernelError(f"gated_act: unknown activation '{activation}' (known: {', '.join(sorted(ACTIVATIONS))})")
-    check(lib().gi_gated_act(_dev(gate_up, "gate_up", torch.float32), _dev(out, "out"), dtype_code(out.dtype), T, I,
-                             ACTIVATIONS[activation], _stream()), "gated_act")
+    check(lib().gi_gated_act(_dev(gate_up, "gate_up", torch.float32), _opt(bias, "bias", torch.float32), _dev(out, "out"),
+                             dtype_code(out.dtype), T, I, ACTIVATIONS[activation], float(limit), _stream()), "gated_act")
 
 
 def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: int, q_norm: Optional[torch.Tensor],
@@ -269,6 +273,59 @@ def add_normed(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: floa
     check(lib().gi_add_normed(_dev(y, "y", torch.float32), _dev(weight, "weight", torch.float32), _dev(x, "x", torch.float32),
                               0 if xn_out is None else _dev(xn_out, "xn_out"), F32 if xn_out is None else dtype_code(xn_out.dtype),
                               n, D, float(eps), int(bool(clear_y)), _stream()), "add_normed")
+
+
+def add_rows_at(x: torch.Tensor, table: torch.Tensor, index: torch.Tensor) -> None:
+    """x[t, :] += table[index[t], :] in 32-bit (a learned vector per position added to the embedding's output)."""
+    T, D = x.shape
+    if table.dim() != 2 or table.shape[1] != D or index.numel() != T:
+        raise KernelError("add_rows_at: shapes of x, table and index do not agree")
+    check(lib().gi_add_rows_at(_dev(x, "x", torch.float32), _dev(table, "table"), dtype_code(table.dtype), _dev(index, "index", torch.int32),
+                               T, D, table.shape[0], _stream()), "add_rows_at")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y[t, :] += bias, 32-bit."""
+    T, D = y.shape
+    if bias.numel() != D:
+        raise KernelError("add_bias: the bias must have one value per column")
+    check(lib().gi_add_bias(_dev(y, "y", torch.float32), _dev(bias, "bias", torch.float32), T, D, _stream()), "add_bias")
+
+
+def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor, gate_offset: int, out: torch.Tensor) -> None:
+    """out[t, c] = a[t, c] * sigmoid(gate[t, gate_offset + c]); a and gate 32-bit, out 32-bit or bfloat16."""
+    T, N = a.shape
+    if out.shape != a.shape or gate.dim() != 2 or gate.shape[0] != T or gate_offset + N > gate.shape[1]:
+        raise KernelError("sigmoid_gate: shapes do not agree")
+    check(lib().gi_sigmoid_gate(_dev(a, "a", torch.float32), _dev(gate, "gate", torch.float32), gate.shape[1], int(gate_offset),
+                                _dev(out, "out"), dtype_code(out.dtype), T, N, _stream()), "sigmoid_gate")
+
+
+def softcap(z: torch.Tensor, cap: float) -> None:
+    """z <- cap * tanh(z / cap) in place, 32-bit."""
+    check(lib().gi_softcap(_dev(z, "z", torch.float32), z.numel(), float(cap), _stream()), "softcap")
+
+
+def depth_mix(x: torch.Tensor, y: torch.Tensor, mult: float, history: Optional[torch.Tensor] = None, slot: int = 0,
+              weights: Optional[torch.Tensor] = None, first: bool = False, next_weight: Optional[torch.Tensor] = None,
+              eps: float = 0.0, xn_out: Optional[torch.Tensor] = None) -> None:
+    """The end of a layer whose sublayers were summed into ``y``: fresh = x + mult * y and y = 0. With ``history``
+    [T, slots, D] (every layer's fresh result, slot 0 what the first layer read: written too when ``first``) and
+    ``weights`` [slot + 1]: history[:, slot] = fresh and x = sum_j weights[j] * history[:, j] over j <= slot; without,
+    x = fresh. ``xn_out``: also next_weight[0] * x / sqrt(mean(x^2) + eps) in xn_out's dtype (the next layer's normed
+    input when its norm has a single weight)."""
+    T, D = x.shape
+    if y.shape != x.shape or (xn_out is not None and xn_out.shape != x.shape):
+        raise KernelError("depth_mix: shapes do not agree")
+    slots = 0
+    if history is not None:
+        if history.dim() != 3 or history.shape[0] != T or history.shape[2] != D or weights is None or weights.numel() != slot + 1:
+            raise KernelError("depth_mix: the history must be [T, slots, D] and the layer needs slot + 1 weights")
+        slots = history.shape[1]
+    check(lib().gi_depth_mix(_dev(x, "x", torch.float32), _dev(y, "y", torch.float32), float(mult), _opt(history, "history", torch.float32),
+                             slots, int(slot), _opt(weights, "weights", torch.float32), int(bool(first)),
+                             _opt(next_weight, "next_weight", torch.float32), float(eps), 0 if xn_out is None else _dev(xn_out, "xn_out"),
+                             F32 if xn_out is None else dtype_code(xn_out.dtype), T, D, _stream()), "depth_mix")
 
 
 def latent_store(proj: torch.Tensor, q_offset: int, q_weight: Optional[torch.Tensor], q_latent: Optional[torch.Tensor],
@@ -475,6 +532,27 @@ def route(x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], 
     count_launches(1)
 
 
+def route_table(tokens: torch.Tensor, feedback: Optional[torch.Tensor], table: torch.Tensor, experts: int, ids: torch.Tensor,
+                weights: torch.Tensor, sorted_rows: torch.Tensor, tile_group: torch.Tensor, n_tiles: torch.Tensor,
+                tile_rows: Optional[int] = None, pair_row: Optional[torch.Tensor] = None) -> None:
+    """Experts fixed per token id: ids[t, :] = table[tokens[t], :] (``table`` [vocab, top] int32; a token given as
+    -(k + 1) stands for feedback[k]), every weight 1 / top; then the bucketing of ``route``. Two launches."""
+    T = tokens.numel()
+    vocab, top = table.shape
+    max_tiles = tile_group.numel()
+    tm = tile_rows or grouped_tile_rows()
+    if ids.shape != (T, top) or weights.shape != (T, top):
+        raise KernelError("route_table: shapes do not agree")
+    if sorted_rows.numel() < max_tiles * tm or max_tiles < route_tiles(T, top, experts, tm) or (pair_row is not None and pair_row.numel() < T * top):
+        raise KernelError("route_table: the buffers of the tiles are too small")
+    check(lib().gi_route_table(_dev(tokens, "tokens", torch.int32), _opt(feedback, "feedback", torch.int32), _dev(table, "table", torch.int32),
+                               vocab, T, int(experts), top, _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+                               _dev(sorted_rows, "sorted_rows", torch.int32), _dev(tile_group, "tile_group", torch.int32),
+                               _dev(n_tiles, "n_tiles", torch.int32), max_tiles, tm, _opt(pair_row, "pair_row", torch.int32), _stream()),
+          "route_table")
+    count_launches(1)
+
+
 def gather_rows(x: torch.Tensor, a_div: int, sorted_rows: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int, out: torch.Tensor) -> None:
     """out[r] = x[sorted_rows[r] // a_div] for the rows of the first n_tiles tiles (zeros where sorted_rows is -1)."""
     if out.shape[1] != x.shape[1] or out.dtype != x.dtype or sorted_rows.numel() < out.shape[0]:
@@ -484,7 +562,7 @@ def gather_rows(x: torch.Tensor, a_div: int, sorted_rows: torch.Tensor, n_tiles:
 
 
 def expert_product_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, n_tiles: torch.Tensor,
-                      gated: Optional[str] = None) -> None:
+                      gated: Optional[str] = None, limit: float = 0.0) -> None:
     """The same on the tensor cores (bfloat16) for rows already in the tiles' order: ``a`` [tiles * 128, K], tile i
     multiplies ``w[tile_group[i]]``; ``out`` [tiles * 128, N] 32-bit, or gated: bfloat16 act(gate) * up."""
     E, rows, K = w.shape
@@ -499,7 +577,7 @@ def expert_product_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_
                                    _dev(out, "out", torch.bfloat16 if gated else torch.float32),
                                    (2 | (ACTIVATIONS[gated] << 8)) if gated else 0, M, N, K, E,
                                    _dev(tile_group, "tile_group", torch.int32), _dev(n_tiles, "n_tiles", torch.int32),
-                                   st.status.data_ptr(), _stream()), "expert_product_tc")
+                                   st.status.data_ptr(), float(limit), _stream()), "expert_product_tc")
 
 
 def expert_product_tc_supported(N: int, K: int, gated: bool) -> bool:
@@ -508,7 +586,7 @@ def expert_product_tc_supported(N: int, K: int, gated: bool) -> bool:
 
 
 def expert_product(a: torch.Tensor, a_div: int, w: torch.Tensor, out: torch.Tensor, sorted_rows: torch.Tensor,
-                   tile_group: torch.Tensor, n_tiles: torch.Tensor, gated: Optional[str] = None) -> None:
+                   tile_group: torch.Tensor, n_tiles: torch.Tensor, gated: Optional[str] = None, limit: float = 0.0) -> None:
     """out[pair] = W[expert of pair] a[pair // a_div] for the pairs that ``route`` bucketed, ``w`` [E, N, K] (gated:
     [E, 2N, K], gate rows first, and out = act(gate) * up with ``gated`` one of ACTIVATIONS)."""
     E, rows, K = w.shape
@@ -518,7 +596,7 @@ def expert_product(a: torch.Tensor, a_div: int, w: torch.Tensor, out: torch.Tens
     if gated is not None and gated not in ACTIVATIONS:
         raise KernelError(f"expert_product: unknown activation '{gated}'")
     check(lib().gi_expert_product(_dev(a, "a"), dtype_code(a.dtype), K, int(a_div), _dev(w, "w"), dtype_code(w.dtype), rows * K, K,
-                                  N * K if gated else 0, int(gated is not None), ACTIVATIONS.get(gated, 0), _dev(out, "out"),
+                                  N * K if gated else 0, int(gated is not None), ACTIVATIONS.get(gated, 0), float(limit), _dev(out, "out"),
                                   dtype_code(out.dtype), N, N, K, _dev(tile_group, "tile_group", torch.int32),
                                   _dev(sorted_rows, "sorted_rows", torch.int32), _dev(n_tiles, "n_tiles", torch.int32),
                                   tile_group.numel(), _stream()), "expert_product")
@@ -998,7 +1076,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16),
                                           _dev(out, "out", torch.float32), 1 if accumulate else 0, M, N, K, K, K, N,
                                           block_q, st.status.data_ptr(), splits, st.workspace.data_ptr() if splits > 1 else 0,
-                                          st.workspace.numel() if splits > 1 else 0, _paired(M, block_q), _stream()), "gemm_tc")
+                                          st.workspace.numel() if splits > 1 else 0, _paired(M, block_q), 0.0, 0, _stream()), "gemm_tc")
         if splits > 1:
             count_launches(1)     # the kernel that adds the ranges up
         return
@@ -1016,20 +1094,23 @@ def gemm_swiglu_supported(M: int, I: int, K: int) -> bool:
     return M > 128 and K % 8 == 0 and I % 8 == 0
 
 
-def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", limit: float = 0.0,
+                bias: Optional[torch.Tensor] = None) -> None:
     """out[M, I] = act(a @ w_gate^T) * (a @ w_up^T) as bfloat16, w_gate_up = [gate rows; up rows]
     [2I, K]: one tensor-core kernel whose epilogue applies the activation (the [M, 2I] intermediate
-    never exists in memory). ``activation``: one of ACTIVATIONS."""
+    never exists in memory). ``activation``: one of ACTIVATIONS (``limit``: see gated_act); ``bias`` [2I] 32-bit is added
+    to the gate and up values before the activation."""
     if activation not in ACTIVATIONS:
         raise KernelError(f"gemm_swiglu: unknown activation '{activation}'")
     M, K = a.shape
     I = out.shape[1]
-    if w_gate_up.shape != (2 * I, K) or out.shape[0] != M:
+    if w_gate_up.shape != (2 * I, K) or out.shape[0] != M or (bias is not None and bias.numel() != 2 * I):
         raise KernelError("gemm_swiglu: shapes do not agree")
     st = _tc_state(a.device)
     check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w_gate_up, "w_gate_up", torch.bfloat16),
                                       _dev(out, "out", torch.bfloat16), 2 | (ACTIVATIONS[activation] << 8), M, I, K, K, K, I, 256,
-                                      st.status.data_ptr(), 1, 0, 0, _paired(M, 256), _stream()), "gemm_swiglu")
+                                      st.status.data_ptr(), 1, 0, 0, _paired(M, 256), float(limit), _opt(bias, "bias", torch.float32),
+                                      _stream()), "gemm_swiglu")
 
 
 _ROPE_FEW_TOKENS = 64      # up to here the few-token product (weights on the 128-row side, token tiles of at most 32) does

@@ -30,7 +30,7 @@ _SIGNATURES = {
                              c_void_p],
     "gi_scale_cast": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_longlong, c_void_p],
     "gi_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
-    "gi_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "gi_gated_act": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "gi_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_void_p],
@@ -46,13 +46,21 @@ _SIGNATURES = {
     "gi_attention_rows_set_pairs": [c_int],
     "gi_head_product": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p],
-    "gi_expert_product": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_longlong, c_int, c_longlong, c_int, c_int,
+    "gi_expert_product": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_longlong, c_int, c_longlong, c_int, c_int, c_float,
                           c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "gi_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                  c_void_p, c_int, c_int, c_void_p, c_void_p],
     "gi_gather_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "gi_route_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "gi_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "gi_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
+    "gi_route_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_void_p, c_void_p],
+    "gi_add_rows_at": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "gi_add_bias": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "gi_sigmoid_gate": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "gi_softcap": [c_void_p, c_longlong, c_float, c_void_p],
+    "gi_depth_mix": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
+                     c_int, c_int, c_void_p],
     "gi_grouped_tile_rows": [],
     "gi_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -67,7 +75,7 @@ _SIGNATURES = {
                    c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
                    c_void_p],
     "gi_gemm_tc_persistent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                              c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
+                              c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_float, c_void_p, c_void_p],
     "gi_gemm_tc_persistent_rope": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_void_p, c_int, c_void_p],

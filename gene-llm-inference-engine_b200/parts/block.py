@@ -166,6 +166,84 @@ class OutputNormBlock:
             carry["output_norm"] = x.data_ptr()      # y = 0 and xn = x hold for whoever runs next
 
 
+@register_block("parallel")
+class ParallelBlock:
+    """One norm, whose output h both sublayers read, and one residual sum: fresh = x + m (mixer(h) + ff(h)) (``block_params``:
+    ``residual_mult`` m, 1 by default; the layer may lack a feed-forward). With ``depth_slot`` s >= 1 and ``depth_slots`` the
+    stream that goes on is a learned mix of everything so far: with R_0 the stream the first layer read and R_j the fresh
+    result of the layer with slot j, x <- sum over j <= s of ``depth_weights``[j] R_j (weights: ``depth_weights`` [s + 1]);
+    without a slot x <- fresh.
+
+    The stream stays 32-bit. Both sublayers add into ``y``, which is zero when they start; one kernel then forms fresh,
+    keeps it in the step's history [tokens, slots, width], mixes, clears y and, when the next block is of this kind with a
+    norm of a single weight, writes that block's normed input in the same pass (``ctx.carry``)."""
+
+    def __init__(self, layer_spec, weights, build):
+        bp = layer_spec.block_params
+        self.mult = float(bp.get("residual_mult", 1.0))
+        self.slot = int(bp.get("depth_slot", 0))
+        self.slots = int(bp.get("depth_slots", 0))
+        self.mixer_norm = build_part(NORMS, "norm", layer_spec.mixer_norm, sub_weights(weights, "mixer_norm."), build)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, sub_weights(weights, "mixer."), build)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward,
+                                           sub_weights(weights, "feed_forward."), build)
+        self.depth_weights = None
+        if self.slot:
+            if not (1 <= self.slot < self.slots):
+                raise ValueError(f"parallel block: slot {self.slot} lies outside the {self.slots} kept results")
+            w = weights["depth_weights"]
+            if w.numel() != self.slot + 1:
+                raise ValueError(f"parallel block: {w.numel()} depth weights, expected {self.slot + 1}")
+            self.depth_weights = w.reshape(-1).to(device=build.device, dtype=torch.float32).contiguous()
+        self.dtype = build.compute_dtype
+        self._next = None           # the block of the next run, when this kernel can write its normed input
+
+    def followed_by(self, block) -> None:
+        ok = isinstance(block, ParallelBlock) and hasattr(block.mixer_norm, "scalar")
+        if self._next is None and ok:
+            self._next = block
+        elif self._next is not block:
+            self._next = False      # several successors (a layer that runs more than once): nothing is prepared
+
+    def forward(self, ctx, run, x: torch.Tensor) -> None:
+        from ..ops import kernels
+        T, D = x.shape
+        y = ctx.scratch("parallel_y", (T, D), torch.float32)
+        xn = ctx.scratch("normed", (T, D), self.dtype)
+        hist = ctx.scratch("depth_history", (T, self.slots, D), torch.float32) if self.slot else None
+        carry = getattr(ctx, "carry", None)
+        state = carry.get("parallel") if carry is not None else None
+        # what the block before left: y = 0 everywhere, xn = this block's normed input, the history filled up to its slot
+        ready = state is not None and state[0] == x.data_ptr() and state[1] is self
+        first = self.slot and not (state is not None and state[0] == x.data_ptr() and state[2])
+        nxt = self._next if self._next else None
+
+        def layer():
+            if not ready:
+                if state is None or state[0] != x.data_ptr():
+                    kernels.scale_cast(x, y, None, 0.0)                          # y = 0
+                self.mixer_norm.forward(x, xn)
+            self.mixer.forward(ctx, run, xn, y)
+            if self.feed_forward is not None:
+                self.feed_forward.forward(ctx, xn, y)
+            kernels.depth_mix(x, y, self.mult, hist, self.slot, self.depth_weights, first=bool(first),
+                              next_weight=nxt.mixer_norm.scalar if nxt else None, eps=nxt.mixer_norm.eps if nxt else 0.0,
+                              xn_out=xn if nxt else None)
+
+        parts = [(self.mixer_norm, None), (self.mixer, run)] + ([(self.feed_forward, None)] if self.feed_forward is not None else [])
+        key = _launch_key(ctx, *parts)
+        if key is not None:
+            ctx.recorded(self, ("layer", run, T, ready, bool(first), state is None or state[0] != x.data_ptr()) + key, layer)
+        else:
+            layer()
+        ctx.tap("attn_out", run.layer, x)
+        ctx.tap("ffn_out", run.layer, x)
+        if carry is not None:
+            carry["parallel"] = (x.data_ptr(), nxt, bool(self.slot))
+
+
 def build_extra(layer_spec, key: str, table, what: str, weights, build):
     """Builds the part that a layer's ``extra`` names ``key`` (for arrangements with more parts than
     the usual four), with the weights under ``<key>.``."""

@@ -14,7 +14,7 @@ import torch
 from ..config import ModelSpec
 from ..ops import kernels
 from ..ops.linear import Linear
-from .registry import BLOCKS, LOGIT_TRANSFORMS, NORMS, BuildContext, build_part, sub_weights
+from .registry import BLOCKS, LOGIT_TRANSFORMS, NORMS, POSITION_ENCODINGS, BuildContext, build_part, sub_weights
 
 
 @dataclass(frozen=True)
@@ -47,6 +47,11 @@ class DecoderModel:
             raise ValueError(f"embedding has shape {tuple(emb.shape)}, expected ({spec.vocab_size}, {spec.hidden_size})")
         self.embedding = emb.to(device=device, dtype=compute_dtype).contiguous()
         self.embedding_scale = spec.embedding_scale
+        # what is added to the embedding's output per position (``add_to(ctx, x)``); most designs: nothing
+        self.embedding_position = None
+        if spec.embedding_position is not None:
+            self.embedding_position = build_part(POSITION_ENCODINGS, "position encoding", spec.embedding_position,
+                                                 sub_weights(params, "embedding_position."), build)
 
         self.layers: List[object] = []
         for i, layer_spec in enumerate(spec.layers):
@@ -61,6 +66,11 @@ class DecoderModel:
         self.runs = [LayerRun(e.layer, e.layer if e.cache_of is None else e.cache_of, e.writes_cache)
                      for e in spec.schedule]
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, sub_weights(params, "final_norm."), build)
+        # a block may prepare what the block of the next run reads (its normed input): it is told who follows
+        for run, after in zip(self.runs, self.runs[1:]):
+            follows = getattr(self.layers[run.layer], "followed_by", None)
+            if follows is not None:
+                follows(self.layers[after.layer])
         if spec.tie_word_embeddings:
             self.head = Linear.over(self.embedding, tiles=weight_tiles)   # the table itself, not a second row-major copy
         else:
@@ -114,6 +124,7 @@ class DecoderModel:
                     visit(v)
 
         visit(self.embedding)
+        visit(self.embedding_position)
         visit(self.layers)
         visit(self.final_norm)
         visit(self.head)
@@ -130,6 +141,8 @@ class DecoderModel:
         x = ctx.scratch("residual", (T, self.hidden_size), torch.float32)
         with ctx.range("embedding"):
             kernels.embed(self.embedding, ctx.tokens, x, self.embedding_scale, ctx.feedback)
+            if self.embedding_position is not None:
+                self.embedding_position.add_to(ctx, x)
         ctx.tap("embedding", -1, x)
         for run in self.runs:
             with ctx.range(f"layer {run.layer}"):

@@ -35,3 +35,20 @@ class RMSNorm:
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         kernels.rmsnorm(x, self.weight, out, self.eps, rows)
         return out
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """out = g * (x / sqrt(mean(x^2) + eps)) with a single learned number g for all coordinates. Params: ``size``,
+    ``eps``. Weights: ``weight``, one value (any shape). It runs the RMSNorm kernel over g repeated ``size`` times;
+    ``scalar`` keeps the one number on the device for kernels that apply the norm themselves."""
+
+    not_weights = ("weight",)       # g repeated: the model's weight is ``scalar``
+
+    def __init__(self, params, weights, build):
+        g = weights["weight"]
+        if g.numel() != 1:
+            raise ValueError(f"rmsnorm_scalar: the weight has {g.numel()} values, expected one")
+        size = int(params["size"])
+        super().__init__(params, {"weight": g.reshape(1).float().expand(size)}, build)
+        self.scalar = g.reshape(1).to(device=build.device, dtype=torch.float32).contiguous()

@@ -6,7 +6,7 @@ import math
 import numpy as np
 import torch
 
-from .registry import register_position_encoding
+from .registry import register_logit_transform, register_position_encoding
 
 
 def rope_frequencies(head_dim: int, theta: float, scaling, rotary_dim=None) -> np.ndarray:
@@ -119,3 +119,41 @@ class RotaryOnDevice:
             freq = freq / factor * r + freq * (1.0 - r)
             self.amplitude = 0.1 * math.log(factor) + 1.0
         self.freq = torch.from_numpy(freq.astype(np.float32)).to(build.device).contiguous()
+
+
+@register_position_encoding("learned")
+class LearnedPosition:
+    """A learned vector per position, added to the embedding's output (not scaled); queries and keys are not rotated.
+    Params: ``size`` (the model's width), ``positions`` (rows of the table: no position beyond it exists). Weights:
+    ``table`` [positions, size]. The model calls ``add_to(ctx, x)`` once per step, after the embedding."""
+
+    applies = "embedding"
+    cos = sin = None
+    interleaved = False
+
+    def __init__(self, params, weights, build):
+        size, rows = int(params["size"]), int(params["positions"])
+        table = weights["table"]
+        if tuple(table.shape) != (rows, size):
+            raise ValueError(f"learned positions: the table has shape {tuple(table.shape)}, expected ({rows}, {size})")
+        if build.max_position > rows:
+            raise ValueError(f"learned positions: the table has {rows} rows, the context length is {build.max_position}")
+        self.table = table.to(device=build.device, dtype=build.compute_dtype).contiguous()
+
+    def add_to(self, ctx, x: torch.Tensor) -> None:
+        from ..ops import kernels
+        kernels.add_rows_at(x, self.table, ctx.positions)
+
+
+@register_logit_transform("softcap")
+class SoftCap:
+    """logits <- cap * tanh(logits / cap), in place, 32-bit. Params: ``cap`` (> 0)."""
+
+    def __init__(self, params, weights, build):
+        self.cap = float(params["cap"])
+        if not self.cap > 0:
+            raise ValueError("softcap: the cap must be positive")
+
+    def forward(self, ctx, logits: torch.Tensor) -> None:
+        from ..ops import kernels
+        kernels.softcap(logits, self.cap)

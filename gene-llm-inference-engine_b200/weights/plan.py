@@ -215,6 +215,69 @@ def gekupel_weight_plan(cfg) -> WeightPlan:
     return WeightPlan(rules, [], assemble)
 
 
+def pinorax_weight_plan(cfg) -> WeightPlan:
+    """Tensor names and shapes of a Pinorax checkpoint: ``embed``, ``pos`` (a vector per position), ``head``, ``final.norm``
+    (a single number) and, for layer i, ``l<i>.norm1`` (a single number), ``l<i>.dwa`` (the i + 2 weights of its depth mix),
+    the mixer's tensors under ``l<i>.mix.`` and the feed-forward's under ``l<i>.mlp.`` (dense: ``gate``, ``up``, ``down`` with a
+    bias ``.b`` each; a mixture: ``e<k>.gate`` / ``.up`` / ``.down`` per expert, ``table`` [vocab, top] of expert indices and
+    ``shared.gate`` / ``.up`` / ``.down``). Projections that read the same input become one product: [q; dkv; g] of the
+    mixer, [gate; up] of a feed-forward; the experts' matrices are stacked."""
+    D, V = cfg.width, cfg.vocab
+    rules = [TensorRule("embed", (V, D)), TensorRule("pos", (cfg.max_positions, D)), TensorRule("head", (V, D)),
+             TensorRule("final.norm", (), "vector")]
+    for i, layer in enumerate(cfg.layers):
+        p, m = f"l{i}.", layer.mixer
+        rules += [TensorRule(p + "norm1", (), "vector"),
+                  TensorRule(p + "mix.q", (m.heads * m.dim, D)), TensorRule(p + "mix.dkv", (m.kv_rank, D)),
+                  TensorRule(p + "mix.dkv.norm", (m.kv_rank,), "vector"), TensorRule(p + "mix.uk", (m.heads * m.dim, m.kv_rank)),
+                  TensorRule(p + "mix.uv", (m.heads * m.vdim, m.kv_rank)), TensorRule(p + "mix.sink", (m.heads,), "vector", (0.0, 1.0)),
+                  TensorRule(p + "mix.g", (m.heads * m.vdim, D)), TensorRule(p + "mix.o", (D, m.heads * m.vdim))]
+        f = layer.mlp
+        if f is not None and f.kind == "dense":
+            for name, shape in (("gate", (f.ff, D)), ("up", (f.ff, D)), ("down", (D, f.ff))):
+                rules += [TensorRule(p + "mlp." + name, shape), TensorRule(p + "mlp." + name + ".b", shape[:1], "vector", (0.0, 0.1))]
+        elif f is not None:
+            for e in range(f.experts):
+                q = f"{p}mlp.e{e}."
+                rules += [TensorRule(q + "gate", (f.ff, D)), TensorRule(q + "up", (f.ff, D)), TensorRule(q + "down", (D, f.ff))]
+            rules.append(TensorRule(p + "mlp.table", (V, f.top), "table", ("distinct", f.experts)))
+            if f.shared_ff:
+                q = p + "mlp.shared."
+                rules += [TensorRule(q + "gate", (f.shared_ff, D)), TensorRule(q + "up", (f.shared_ff, D)),
+                          TensorRule(q + "down", (D, f.shared_ff))]
+        rules.append(TensorRule(p + "dwa", (i + 2,), "vector", (1.0 / (i + 2), 0.2)))
+
+    def assemble(t: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {"embedding.weight": t["embed"], "embedding_position.table": t["pos"], "head.weight": t["head"],
+                                        "final_norm.weight": t["final.norm"]}
+        for i, layer in enumerate(cfg.layers):
+            p, q = f"l{i}.", f"layers.{i}."
+            out[q + "mixer_norm.weight"] = t[p + "norm1"]
+            out[q + "depth_weights"] = t[p + "dwa"]
+            a, b = p + "mix.", q + "mixer."
+            out[b + "w_down"] = _cat([t[a + "q"], t[a + "dkv"], t[a + "g"]])
+            out[b + "kv_latent_norm"] = t[a + "dkv.norm"]
+            out[b + "w_uk"], out[b + "w_uv"], out[b + "w_o"], out[b + "sink"] = t[a + "uk"], t[a + "uv"], t[a + "o"], t[a + "sink"]
+            f = layer.mlp
+            if f is None:
+                continue
+            a, b = p + "mlp.", q + "feed_forward."
+            if f.kind == "dense":
+                out[b + "w_gate_up"] = _cat([t[a + "gate"], t[a + "up"]])
+                out[b + "b_gate_up"] = _cat([t[a + "gate.b"], t[a + "up.b"]])
+                out[b + "w_down"], out[b + "b_down"] = t[a + "down"], t[a + "down.b"]
+            else:
+                out[b + "w_gate_up"] = torch.stack([_cat([t[f"{a}e{e}.gate"], t[f"{a}e{e}.up"]]) for e in range(f.experts)])
+                out[b + "w_down"] = torch.stack([t[f"{a}e{e}.down"] for e in range(f.experts)])
+                out[b + "table"] = t[a + "table"]
+                if f.shared_ff:
+                    out[b + "shared.w_gate_up"] = _cat([t[a + "shared.gate"], t[a + "shared.up"]])
+                    out[b + "shared.w_down"] = t[a + "shared.down"]
+        return out
+
+    return WeightPlan(rules, [], assemble)
+
+
 def _cat(parts: List[torch.Tensor]) -> torch.Tensor:
     """Concatenates rows; parts of different stored dtypes are widened to 32-bit first."""
     if len({p.dtype for p in parts}) > 1:

@@ -5,7 +5,7 @@ Every tensor has its own generator seeded from (seed, tensor name), so the value
 the order in which tensors are drawn or on the dtype they are stored in: values are drawn in
 32-bit and rounded to bfloat16 (nearest even) only when stored so. Matrices are N(0, std); norm
 weights are ``norm_mean + N(0, norm_std)``; a tensor whose rule carries ``init`` (a mean and a deviation,
-or a uniform range) is drawn as that says.
+a uniform range, or for an integer table rows of distinct indices) is drawn as that says.
 """
 from __future__ import annotations
 
@@ -42,10 +42,14 @@ def write_random_model(config_json: Dict[str, Any], seed: int, out_dir: str, dty
         for rule in plan.rules:
             g = torch.Generator(device="cpu")
             g.manual_seed(_tensor_seed(seed, rule.name))
-            if rule.kind == "table":
-                yield rule.name, torch.zeros(rule.shape, dtype=torch.int32)
-                continue
             init = getattr(rule, "init", None)
+            if rule.kind == "table":
+                if init is not None and init[0] == "distinct":      # every row: different indices below init[1], in random order
+                    order = torch.rand((rule.shape[0], init[1]), generator=g).argsort(dim=1)
+                    yield rule.name, order[:, :rule.shape[1]].to(torch.int32).contiguous()
+                else:
+                    yield rule.name, torch.zeros(rule.shape, dtype=torch.int32)
+                continue
             if init is not None and init[0] == "uniform":
                 yield rule.name, torch.rand(rule.shape, generator=g, dtype=torch.float32).mul_(init[2] - init[1]).add_(init[1]).to(store)
                 continue
