@@ -7,6 +7,7 @@
     python bench.py --scenario sizes [--shape ...]   (decode steps at a grid of batch sizes and contexts, see run_sizes)
     python bench.py --scenario nipadra               (the Nipadra design beside Llama at equal layer sizes, see run_nipadra)
     python bench.py --scenario gekupel               (the Gekupel design beside Llama at equal layer sizes, see run_gekupel)
+    python bench.py --scenario pinorax               (the Pinorax design beside Gekupel and Llama at equal layer sizes, see run_pinorax)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -811,6 +812,208 @@ def run_gekupel(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- Pinorax beside Gekupel
+def pinorax_config(width, ff, layers, vocab, heads, head_dim, positions):
+    """A Pinorax model with the layer sizes of a Llama shape, made like the latent layers of ``gekupel_config``: half of
+    Llama's heads, a latent of 1/4 of the width (at most 512). The first layer has a dense feed-forward, the others a
+    mixture of 8 experts of 3/8 of the dense width of which a token uses 2, with a shared expert of 1/4 of it (together
+    the dense layer's multiply-adds per token)."""
+    mixer = {"dim": head_dim, "heads": max(heads // 2, 1), "kv_rank": min(512, width // 4), "scale": head_dim ** -0.5, "vdim": head_dim}
+    moe = {"expert": {"ff": 3 * ff // 8, "limit": 7.0}, "kind": "moe", "router": {"experts": 8, "top": 2},
+           "shared": {"ff": ff // 4, "limit": 7.0}}
+    kinds = [{"mixer": mixer, "mlp": {"ff": ff, "kind": "dense"}, "type": "latent_attention"}] + \
+        [{"mixer": mixer, "mlp": moe, "type": "latent_attention"}] * 3
+    return {"architecture": "Pinorax", "layers": [kinds[i % 4] for i in range(layers)], "logit_softcap": 30.0,
+            "max_positions": positions, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "vocab": vocab, "width": width}
+
+
+def pinorax_kernel_table(width, heads, head_dim, ff, vocab, layers, T, pk):
+    """Each kernel that the Pinorax design added or changed, alone, beside the like kernel of the Gekupel path (the
+    closest existing design), at the sizes of one layer: a prompt portion of ``T`` tokens of one request and a decode
+    step of 8 requests at a context of ``T``. ``frac`` is the time the kernel's algorithmic bytes (or, where larger, its
+    multiply-adds at the tensor cores' measured rate) need, divided by the time it took; ``frac_of_32bit_issue`` the
+    same against the CUDA cores' 32-bit rate, for kernels whose arithmetic has to stay 32-bit."""
+    import torch
+    from geneinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    props = torch.cuda.get_device_properties(dev)
+    simt_ops = props.multi_processor_count * 128 * 1.965e9
+    bf = torch.bfloat16
+
+    def add(name, like, fn, nbytes, flops=0.0, simt=0.0):
+        ms = time_calls(fn, flush=flush)
+        ideal = max(nbytes / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e3
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1), "frac": round(ideal / ms, 3)}
+        if simt:
+            row["frac_of_32bit_issue"] = round(simt / simt_ops * 1e3 / ms, 3)
+        rows.append(row)
+
+    D, page = width, 16
+    lh, kr = max(heads // 2, 1), min(512, width // 4)
+    E, top, I, Is = 8, 2, 3 * ff // 8, ff // 4
+    slots, slot = layers + 1, max(layers // 2, 1)
+    for what, R, n in (("prefill", 1, T), ("decode", 8, 1)):
+        N = R * n
+        i32 = dict(dtype=torch.int32, device=dev)
+        rr = torch.arange(R, **i32).repeat_interleave(n)
+        n_pages = R * ((T + page - 1) // page)
+        tables = torch.arange(n_pages, **i32).view(R, -1)
+        pos = (torch.arange(n, **i32) + (T - n)).repeat(R)
+        x, y = torch.randn(N, D, device=dev), torch.randn(N, D, device=dev)
+        xn = torch.empty(N, D, dtype=bf, device=dev)
+        w, one = torch.ones(D, device=dev), torch.ones(1, device=dev)
+        hist = torch.randn(N, slots, D, device=dev)
+        dw, bias = torch.rand(slot + 1, device=dev), torch.randn(D, device=dev)
+        add(f"depth_mix, {slot + 1} terms, bias, next norm ({what})", "add_normed",
+            lambda: K.depth_mix(x, y, 0.5, hist, slot, dw, next_weight=one, eps=1e-6, xn_out=xn, y_bias=bias), N * D * (4 * slot + 22))
+        add(f"add_normed, Gekupel ({what})", "", lambda: K.add_normed(y, w, x, 1e-6, xn_out=xn, clear_y=True), N * D * 18)
+        ptab = torch.randn(T, D, device=dev).to(bf)
+        add(f"add_rows_at, learned positions ({what})", "embed", lambda: K.add_rows_at(x, ptab, pos), N * D * 10)
+        etab = torch.randn(vocab, D, device=dev).to(bf)
+        toks = torch.randint(0, vocab, (N,), **i32)
+        add(f"embed, Gekupel ({what})", "", lambda: K.embed(etab, toks, x), N * D * 6)
+        # latent attention: store, queries through the heads' key matrices, attention over all latent rows, values and gate
+        cols = lh * head_dim + kr + lh * head_dim
+        down = torch.randn(N, cols, device=dev)
+        cache = torch.randn(n_pages, 1, page, kr, device=dev).to(bf)
+        wc = torch.ones(kr, device=dev)
+        add(f"latent_store, no query latent ({what})", "latent_store",
+            lambda: K.latent_store(down, 0, None, None, lh * head_dim, wc, lh * head_dim + kr, None, 1.0, 1e-6, pos, rr, tables, cache, page),
+            N * kr * 6)
+        wuk = (torch.randn(lh, kr, head_dim, device=dev) * 0.05).to(bf)
+        qa = torch.empty(N, lh * kr, device=dev)
+        add(f"head_product, queries from the first product ({what})", "head_product",
+            lambda: K.head_product(down, 0, head_dim, wuk, qa, 0, kr), lh * kr * head_dim * 2 + N * lh * (head_dim + kr) * 4,
+            flops=2.0 * N * lh * kr * head_dim, simt=N * lh * kr * head_dim)
+        ol = torch.empty(N, lh * kr, device=dev)
+        sinks = torch.randn(lh, device=dev)
+        pt = K.attention_rows_tile_tokens(lh, 1, kr, kr, True)
+
+        def listed(span):
+            if n == 1:
+                kw = {"rows": torch.arange(R, **i32)}
+                count = R
+            else:
+                kw = {"tiles": torch.tensor([(t, min(pt, n - t), 0) for t in range(0, n, pt)][::-1], **i32)}
+                count = kw["tiles"].shape[0]
+            sp = K.attention_rows_splits(count, lh, 1, span)
+            if sp > 1:
+                kw.update(splits=sp, workspace=torch.empty(K.attention_rows_workspace_rows(count, lh, 1, sp), kr + 2, device=dev))
+            return kw
+
+        for name, like, window in ((f"attention_rows over the latent, all {T} positions, sink ({what})", "attention_rows", None),
+                                   (f"attention_rows over the latent, window {T // 2}, Gekupel ({what})", "", T // 2)):
+            kw = listed(window or T)
+            seen = sum(min(window or T, p + 1) for p in range(T - n, T))
+            add(name, like, lambda: K.attention_rows(qa, cache, None, ol, rr, pos, tables, lh, 1, kr, kr, page, 0.1, window=window,
+                                                     sinks=sinks, **kw),
+                R * min(T, (window or T) + n) * kr * 2 + N * lh * 2 * kr * 4, flops=2.0 * R * seen * lh * 2 * kr)
+        wuv = (torch.randn(lh, head_dim, kr, device=dev) * 0.05).to(bf)
+        att = torch.empty(N, lh * head_dim, dtype=bf, device=dev)
+        for name, like, gate in ((f"head_product, values with the output gate ({what})", "head_product", down),
+                                 (f"head_product, values, Gekupel ({what})", "", None)):
+            add(name, like, lambda: K.head_product(ol, 0, kr, wuv, att, 0, head_dim, gate=gate, gate_offset=lh * head_dim + kr),
+                lh * kr * head_dim * 2 + N * lh * (kr * 4 + head_dim * (6 if gate is not None else 2)), flops=2.0 * N * lh * kr * head_dim,
+                simt=N * lh * kr * head_dim)
+        # experts chosen by a table beside experts chosen by scores; the capped activation beside SiLU
+        router, corr = torch.randn(E, D, device=dev) * 0.1, torch.zeros(E, device=dev)
+        table = torch.rand(vocab, E, device=dev).argsort(1)[:, :top].to(torch.int32).contiguous()
+        wgu = (torch.randn(E, 2 * I, D, device=dev) * 0.02).to(bf)
+        wd = (torch.randn(E, D, I, device=dev) * 0.02).to(bf)
+        xb = torch.randn(N, D, device=dev).to(bf)
+        ids, wts = torch.empty(N, top, **i32), torch.empty(N, top, device=dev)
+        cnt = torch.empty(1, **i32)
+        tc = N * top >= 256
+        tm = K.TC_TILE_ROWS if tc else K.grouped_tile_rows()
+        tiles = K.route_tiles(N, top, E, tm)
+        srt, grp, prow = torch.empty(tiles * tm, **i32), torch.empty(tiles, **i32), torch.empty(N * top, **i32)
+        add(f"route + bucket, Gekupel ({what})", "", lambda: K.route(xb, router, corr, top, ids, wts, srt, grp, cnt, tile_rows=tm, pair_row=prow),
+            N * D * 2 + E * D * 4)
+        add(f"route_table + bucket ({what})", "route", lambda: K.route_table(toks, None, table, E, ids, wts, srt, grp, cnt, tile_rows=tm, pair_row=prow),
+            N * (4 + 12 * top))
+        used = int(cnt.item())
+        hit = len(set(ids.view(-1).tolist()))
+        for act, like, limit in (("capped_swish", "experts", 7.0), ("silu", "", 0.0)):
+            who = "" if like else ", Gekupel"
+            if tc:
+                rows_x = torch.randn(tiles * tm, D, device=dev).to(bf)
+                hid = torch.empty(tiles * tm, I, dtype=bf, device=dev)
+                add(f"experts [gate; up] on the tensor cores, {act}{who} ({what})", like,
+                    lambda: K.expert_product_tc(rows_x, wgu, hid, grp, cnt, gated=act, limit=limit),
+                    hit * 2 * I * D * 2 + used * tm * (D + I) * 2, flops=2.0 * N * top * 2 * I * D)
+            else:
+                hid = torch.empty(N * top, I, device=dev)
+                add(f"experts [gate; up], tiles of 16 rows, {act}{who} ({what})", like,
+                    lambda: K.expert_product(xb, top, wgu, hid, srt, grp, cnt, gated=act, limit=limit), hit * 2 * I * D * 2,
+                    simt=used * 16 * 2 * I * D)
+        # the dense feed-forward with biases (and the shared expert's capped activation) beside the plain one
+        wg = (torch.randn(2 * ff, D, device=dev) * 0.02).to(bf)
+        b2 = torch.randn(2 * ff, device=dev)
+        hd_ = torch.empty(N, ff, dtype=bf, device=dev)
+        if K.gemm_swiglu_supported(N, ff, D):
+            for name, like, kw in ((f"[gate; up] product with biases and SiLU ({what})", "gemm_swiglu", dict(bias=b2)),
+                                   (f"[gate; up] product with the capped activation ({what})", "gemm_swiglu", dict(activation="capped_swish", limit=7.0)),
+                                   (f"[gate; up] product with SiLU, Gekupel ({what})", "", {})):
+                add(name, like, lambda: K.gemm_swiglu(xb, wg, hd_, **kw), 2 * ff * D * 2 + N * (D + ff) * 2, flops=2.0 * N * 2 * ff * D)
+        else:
+            gu = torch.randn(N, 2 * ff, device=dev)
+            add(f"gated_act with biases ({what})", "swiglu", lambda: K.gated_act(gu, hd_, "silu", 0.0, b2), N * ff * 10 + ff * 8)
+            add(f"gated_act, capped ({what})", "swiglu", lambda: K.gated_act(gu, hd_, "capped_swish", 7.0), N * ff * 10)
+            add(f"swiglu, Gekupel ({what})", "", lambda: K.swiglu(gu, hd_), N * ff * 10)
+        logits = torch.randn(R, vocab, device=dev)
+        add(f"softcap of {R} rows of logits ({what})", "", lambda: K.softcap(logits, 30.0), R * vocab * 8)
+        del wg, wgu, wd
+    return rows
+
+
+def run_pinorax(args):
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 at context 2,048) throughput of Pinorax models
+    whose layers have the sizes of the Llama-3.2-1B and Llama-3.1-8B shapes (four layers each, random bf16 weights),
+    beside Gekupel models (the closest existing design: latent attention and routed experts; their windows and blocks
+    set to the whole context, so that both see as many keys) and Llama models of the same sizes; then every kernel
+    that the design added or changed alone beside the like kernel of the Gekupel path. Prints one JSON line."""
+    import torch
+    from geneinfer_b200 import Engine
+    from geneinfer_b200.weights import write_random_model
+    pk = peaks()
+    layers = args.layers or 4
+    context, batch, T = 2048, 8, PREFILL_TOKENS
+    models = []
+    for name, base in (("1b", LLAMA_1B), ("8b", LLAMA_8B)):
+        llama = dict(base, num_hidden_layers=layers, tie_word_embeddings=True)
+        gek = gekupel_config(base["hidden_size"], base["intermediate_size"], layers, base["vocab_size"], base["num_attention_heads"],
+                             base["head_dim"], base["num_key_value_heads"], context)
+        pin = pinorax_config(base["hidden_size"], base["intermediate_size"], layers, base["vocab_size"], base["num_attention_heads"],
+                             base["head_dim"], context)
+        for arch, cfg in (("Llama", llama), ("Gekupel", gek), ("Pinorax", pin)):
+            if arch == "Llama":
+                folder = model_folder(cfg)
+            else:
+                folder = os.path.join(tempfile.gettempdir(), f"geneinfer_bench_{arch.lower()}_{name}_{layers}_{context}_{os.getuid()}")
+                if not os.path.isfile(os.path.join(folder, "done")):
+                    write_random_model(cfg, 1, folder, "bfloat16", std=0.02)
+                    open(os.path.join(folder, "done"), "w").close()
+            llm = Engine(folder, dtype="bfloat16", max_seq_len=context, page_size=PAGE, kv_pages=batch * (context // PAGE),
+                         max_running=batch, step_tokens=T, prefix_cache=False)
+            vocab = base["vocab_size"]
+            ms_prefill = time_prefill(llm.steps, T, 2, vocab)
+            ms_decode, _ = time_decode_device(llm.steps, batch, context, args.steps, args.warmup, vocab)
+            llm.steps.check_status()
+            models.append({"model": f"{arch} at the {SHAPES[name][0]} layer sizes, {layers} layers",
+                           "prefill_2048_tok_s": round(T / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                           "decode_b8_ctx2048_tok_s": round(batch / ms_decode * 1e3, 1), "decode_ms_per_step": round(ms_decode, 4),
+                           "weight_gb": round(llm.model.weight_bytes() / 1e9, 3)})
+            del llm
+            torch.cuda.empty_cache()
+    table = pinorax_kernel_table(2048, 32, 64, 8192, 128256, layers, T, pk)
+    print(json.dumps({"metric": "Pinorax beside Gekupel and Llama at equal layer sizes (random bf16 weights)", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "steps": args.steps, "warmup": args.warmup, "peaks": pk["source"],
+                      "peak_gb_s": pk["hbm_gbs"], "peak_tflops": pk["bf16_tflops"], "models": models, "kernels": table}))
+    return 0
+
+
 def run_scenario(args):
     """Two workloads through the entry point, beside the default run: ``mixed`` (32 requests with
     prompts of 128 to 4096 random ids and 256 generated tokens each, admitted together, prompts cut
@@ -1021,7 +1224,7 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="precision of a --scenario run (float32: the requests run alone must give identical tokens)")
-    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra", "gekupel"], default="",
+    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra", "gekupel", "pinorax"], default="",
                     help="a workload through the scheduler (mixed, prefix) or decode steps at a grid of sizes, instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -1036,6 +1239,8 @@ def main():
         return run_nipadra(args)
     if args.scenario == "gekupel":
         return run_gekupel(args)
+    if args.scenario == "pinorax":
+        return run_pinorax(args)
     if args.scenario:
         return run_scenario(args)
     return run_ours(args)

@@ -5,7 +5,8 @@
 //              W[h] = w + h * w_gs [N, K], out's columns o_off + h * o_gs .. + N; optionally ``tail`` more
 //              columns behind a head's K inputs are rotated by the row's position and copied behind its N outputs
 //              (queries of an attention over a shared latent: the plain part goes through the head's key matrix,
-//              the rotated part stays)
+//              the rotated part stays); optionally every output is multiplied by the sigmoid of a gate value of its own
+//              (32-bit, in a row of the token: the heads' outputs of a gated attention)
 //     experts  rows are (token, choice) pairs sorted by expert: tile i belongs to expert tile_group[i], its rows are
 //              sorted_rows[16 i ..] (-1: none); the input row is pair / a_div, the output row the pair;
 //              gated: out = act(W_gate a) * (W_up a) with W[g] = [gate rows; up rows]
@@ -36,7 +37,16 @@ struct GroupedArgs {
     int act; float act_limit;                                     // gated: a GateAct code and its limit
     // rotated tail (heads form)
     int tail; const float* freq; float amplitude; const int* positions;
+    // output gate (heads form): out *= sigmoid(gate[row, gate_off + h * N + n]), 32-bit (else null)
+    const float* gate; long long ldg; int gate_off;
 };
+
+// The element-wise sigmoid gate of the heads form, on output n of head g of row r.
+__device__ __forceinline__ float gp_gated(const GroupedArgs& p, float v, int r, int g, int n) {
+    if (p.gate == nullptr) return v;
+    const float z = p.gate[static_cast<size_t>(r) * p.ldg + p.gate_off + static_cast<size_t>(g) * p.N + n];
+    return v * (1.0f / (1.0f + expf(-z)));
+}
 
 template <typename TA, typename TW, bool GATED>
 __global__ void __launch_bounds__(128)
@@ -130,6 +140,7 @@ grouped_product_kernel(const GroupedArgs p) {
             if (n >= p.N) continue;
             float v = acc[i][j];
             if (GATED) v = gated_value(v, acc_up[U * i][j], p.act, p.act_limit);
+            v = gp_gated(p, v, r, g, n);
             const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
             if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
             else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
@@ -250,6 +261,7 @@ grouped_rows_kernel(const GroupedArgs p) {
                     float v = warp_sum(acc[r][i]);
                     if (GATED) v = gated_value(v, warp_sum(acc_up[GATED ? r : 0][i]), p.act, p.act_limit);
                     if (lane == 0) {
+                        v = gp_gated(p, v, s_row[m0 + i], g, n_first + r);
                         const size_t o = static_cast<size_t>(s_row[m0 + i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n_first + r;
                         if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
                         else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
@@ -336,8 +348,9 @@ head_product64_kernel(const GroupedArgs p) {
             const int n = n0 + tx + j;
             if (n >= p.N) continue;
             const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
-            if (p.out_is_f32) static_cast<float*>(p.out)[o] = acc[i][j];
-            else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(acc[i][j]);
+            const float v = gp_gated(p, acc[i][j], r, g, n);
+            if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
+            else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
         }
     }
 }
@@ -514,9 +527,11 @@ extern "C" int gi_grouped_tile_rows() { return kGpTM; }
 
 static int gi_head_product_impl(const void* a, int a_dtype, long long lda, int a_off, int a_gs, const void* w, int w_dtype,
                                 long long w_gs, void* out, int out_dtype, long long ldo, int o_off, int o_gs, int rows, int heads,
-                                int N, int K, int tail, const float* freq, float amplitude, const int* positions, void* stream) {
+                                int N, int K, int tail, const float* freq, float amplitude, const int* positions, const float* gate,
+                                long long ldg, int gate_off, void* stream) {
     if (rows == 0) return 0;
     GI_REQUIRE(rows > 0 && heads > 0 && N > 0 && K > 0, "head_product: sizes must be positive");
+    GI_REQUIRE(gate == nullptr || (gate_off >= 0 && gate_off + static_cast<long long>(heads) * N <= ldg), "head_product: the gate's columns lie outside its rows");
     GI_REQUIRE(tail >= 0 && tail % 2 == 0 && (tail == 0 || (freq && positions)), "head_product: a rotated tail needs an even size, frequencies and positions");
     GI_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "head_product: unsupported output dtype");
     GroupedArgs p = {};
@@ -525,6 +540,7 @@ static int gi_head_product_impl(const void* a, int a_dtype, long long lda, int a
     p.out = out; p.out_is_f32 = out_dtype == kF32; p.ldo = ldo; p.o_off = o_off; p.o_gs = o_gs;
     p.N = N; p.K = K; p.rows = rows; p.groups = heads;
     p.tail = tail; p.freq = freq; p.amplitude = amplitude; p.positions = positions;
+    p.gate = gate; p.ldg = ldg; p.gate_off = gate_off;
     const long long tiles = static_cast<long long>((rows + kGpTM - 1) / kGpTM) * heads;
     GI_REQUIRE(tiles <= 2147483647LL, "head_product: too many tiles");
     dim3 grid(static_cast<unsigned>(tiles), (N + kGpTN - 1) / kGpTN);
@@ -637,9 +653,10 @@ static int gi_route_combine_impl(const float* part, const float* weights, const 
 
 extern "C" int gi_head_product(const void* a, int a_dtype, long long lda, int a_off, int a_gs, const void* w, int w_dtype,
                                long long w_gs, void* out, int out_dtype, long long ldo, int o_off, int o_gs, int rows, int heads,
-                               int N, int K, int tail, const float* freq, float amplitude, const int* positions, void* stream) {
+                               int N, int K, int tail, const float* freq, float amplitude, const int* positions, const float* gate,
+                               long long ldg, int gate_off, void* stream) {
     return gi::dispatch(gi_head_product_impl, a, a_dtype, lda, a_off, a_gs, w, w_dtype, w_gs, out, out_dtype, ldo, o_off, o_gs, rows,
-                        heads, N, K, tail, freq, amplitude, positions, stream);
+                        heads, N, K, tail, freq, amplitude, positions, gate, ldg, gate_off, stream);
 }
 
 extern "C" int gi_expert_product(const void* a, int a_dtype, long long lda, int a_div, const void* w, int w_dtype, long long w_gs,

@@ -6,8 +6,9 @@
 //   sigmoid_gate    out[t, c] = a[t, c] * sigmoid(g[t, off + c]): an element-wise output gate (out in the compute dtype)
 //   depth_mix       with h [T, slots, D] the results kept so far (slot 0 the embedding's output, slot i + 1 layer i's),
 //                   x the stream that layer i read and y what its sublayers produced:
-//                   h[t, i + 1] = x[t] + m y[t];  x[t] = sum_{j <= i + 1} w[j] h[t, j]   (w: the layer's i + 2 mixing weights);
-//                   without weights x[t] += m y[t]. The same pass clears y and writes the unit-RMS norm of the new x
+//                   h[t, i + 1] = x[t] + m (y[t] + b);  x[t] = sum_{j <= i + 1} w[j] h[t, j]   (w: the layer's i + 2 mixing
+//                   weights; b: an optional bias that a sublayer's last product left to this kernel);
+//                   without weights x[t] += m (y[t] + b). The same pass clears y and writes the unit-RMS norm of the new x
 //                   times one number (the next layer's single norm weight) in the compute dtype.
 //   softcap         z <- cap * tanh(z / cap), in place
 //
@@ -63,7 +64,7 @@ constexpr int kDepthMaxPerThread = 16;      // a row of up to 256 * 16 values is
 // RMSNorm kernels (a fixed strided assignment, a fixed xor tree, the warps in index order).
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-depth_mix_kernel(float* __restrict__ x, float* __restrict__ y, float m, float* __restrict__ hist, int slots, int slot,
+depth_mix_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ y_bias, float m, float* __restrict__ hist, int slots, int slot,
                  const float* __restrict__ w, int first, const float* __restrict__ next_weight, float eps,
                  TOut* __restrict__ xn_out, int D) {
     pdl_prologue();
@@ -75,7 +76,7 @@ depth_mix_kernel(float* __restrict__ x, float* __restrict__ y, float m, float* _
     int n = 0;
     for (int d = threadIdx.x; d < D; d += 256, ++n) {
         const float x_old = x[row + d];
-        const float fresh = x_old + m * y[row + d];
+        const float fresh = x_old + m * (y_bias ? y[row + d] + y_bias[d] : y[row + d]);
         y[row + d] = 0.f;
         float v = fresh;
         if (h) {
@@ -155,17 +156,17 @@ static int gi_softcap_impl(float* z, long long total, float cap, void* stream) {
     return check_launch("softcap");
 }
 
-static int gi_depth_mix_impl(float* x, float* y, float m, float* hist, int slots, int slot, const float* w, int first,
+static int gi_depth_mix_impl(float* x, float* y, const float* y_bias, float m, float* hist, int slots, int slot, const float* w, int first,
                              const float* next_weight, float eps, void* xn_out, int xn_dtype, int T, int D, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && D > 0, "depth_mix: sizes must be positive");
     GI_REQUIRE(hist == nullptr || (w != nullptr && slot >= 1 && slot < slots), "depth_mix: slot %d lies outside the %d kept results", slot, slots);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (xn_dtype == kBF16)
-        launch_kernel((depth_mix_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, x, y, m, hist, slots, slot, w, first, next_weight, eps,
+        launch_kernel((depth_mix_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
                       static_cast<__nv_bfloat16*>(xn_out), D);
     else if (xn_dtype == kF32)
-        launch_kernel((depth_mix_kernel<float>), dim3(T), dim3(256), 0, st, x, y, m, hist, slots, slot, w, first, next_weight, eps,
+        launch_kernel((depth_mix_kernel<float>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
                       static_cast<float*>(xn_out), D);
     else
         GI_REQUIRE(false, "depth_mix: unsupported dtype code %d", xn_dtype);
@@ -188,7 +189,7 @@ extern "C" int gi_softcap(float* z, long long total, float cap, void* stream) {
     return gi::dispatch(gi_softcap_impl, z, total, cap, stream);
 }
 
-extern "C" int gi_depth_mix(float* x, float* y, float m, float* hist, int slots, int slot, const float* w, int first,
+extern "C" int gi_depth_mix(float* x, float* y, const float* y_bias, float m, float* hist, int slots, int slot, const float* w, int first,
                             const float* next_weight, float eps, void* xn_out, int xn_dtype, int T, int D, void* stream) {
-    return gi::dispatch(gi_depth_mix_impl, x, y, m, hist, slots, slot, w, first, next_weight, eps, xn_out, xn_dtype, T, D, stream);
+    return gi::dispatch(gi_depth_mix_impl, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps, xn_out, xn_dtype, T, D, stream);
 }

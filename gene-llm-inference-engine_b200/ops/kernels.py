@@ -308,21 +308,22 @@ def softcap(z: torch.Tensor, cap: float) -> None:
 
 def depth_mix(x: torch.Tensor, y: torch.Tensor, mult: float, history: Optional[torch.Tensor] = None, slot: int = 0,
               weights: Optional[torch.Tensor] = None, first: bool = False, next_weight: Optional[torch.Tensor] = None,
-              eps: float = 0.0, xn_out: Optional[torch.Tensor] = None) -> None:
-    """The end of a layer whose sublayers were summed into ``y``: fresh = x + mult * y and y = 0. With ``history``
+              eps: float = 0.0, xn_out: Optional[torch.Tensor] = None, y_bias: Optional[torch.Tensor] = None) -> None:
+    """The end of a layer whose sublayers were summed into ``y``: fresh = x + mult * y and y = 0 (``y_bias`` [D]: a bias
+    that a sublayer's last product left to this kernel, added to every row of y first). With ``history``
     [T, slots, D] (every layer's fresh result, slot 0 what the first layer read: written too when ``first``) and
     ``weights`` [slot + 1]: history[:, slot] = fresh and x = sum_j weights[j] * history[:, j] over j <= slot; without,
     x = fresh. ``xn_out``: also next_weight[0] * x / sqrt(mean(x^2) + eps) in xn_out's dtype (the next layer's normed
     input when its norm has a single weight)."""
     T, D = x.shape
-    if y.shape != x.shape or (xn_out is not None and xn_out.shape != x.shape):
+    if y.shape != x.shape or (xn_out is not None and xn_out.shape != x.shape) or (y_bias is not None and y_bias.numel() != D):
         raise KernelError("depth_mix: shapes do not agree")
     slots = 0
     if history is not None:
         if history.dim() != 3 or history.shape[0] != T or history.shape[2] != D or weights is None or weights.numel() != slot + 1:
             raise KernelError("depth_mix: the history must be [T, slots, D] and the layer needs slot + 1 weights")
         slots = history.shape[1]
-    check(lib().gi_depth_mix(_dev(x, "x", torch.float32), _dev(y, "y", torch.float32), float(mult), _opt(history, "history", torch.float32),
+    check(lib().gi_depth_mix(_dev(x, "x", torch.float32), _dev(y, "y", torch.float32), _opt(y_bias, "y_bias", torch.float32), float(mult), _opt(history, "history", torch.float32),
                              slots, int(slot), _opt(weights, "weights", torch.float32), int(bool(first)),
                              _opt(next_weight, "next_weight", torch.float32), float(eps), 0 if xn_out is None else _dev(xn_out, "xn_out"),
                              F32 if xn_out is None else dtype_code(xn_out.dtype), T, D, _stream()), "depth_mix")
@@ -474,13 +475,16 @@ def attention_rows_launch_key(ctx, num_heads: int, num_kv_heads: int, head_dim: 
 
 def head_product(a: torch.Tensor, a_offset: int, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_offset: int,
                  out_head_stride: int, tail: int = 0, freq: Optional[torch.Tensor] = None, amplitude: float = 1.0,
-                 positions: Optional[torch.Tensor] = None) -> None:
+                 positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
     """out[t, out_offset + h * out_head_stride + n] = sum_k w[h, n, k] * a[t, a_offset + h * a_head_stride + k] for
     every head h of ``w`` [H, N, K]: a matrix per head, applied to that head's slice of a row. ``tail`` > 0: the tail
     columns behind a head's K inputs are rotated pair by pair by positions[t] * freq[i] (cos and sin times
-    ``amplitude``) and written behind the head's N outputs."""
+    ``amplitude``) and written behind the head's N outputs. ``gate`` [T, ld] 32-bit: output n of head h is multiplied by
+    sigmoid(gate[t, gate_offset + h * N + n]) (an element-wise output gate laid out head by head)."""
     T = a.shape[0]
     H, N, K = w.shape
+    if gate is not None and (gate.dim() != 2 or gate.shape[0] != T or gate_offset < 0 or gate_offset + H * N > gate.shape[1]):
+        raise KernelError("head_product: the gate's columns lie outside its rows")
     if a.dim() != 2 or out.dim() != 2 or out.shape[0] != T:
         raise KernelError("head_product: a and out must be matrices with one row per token")
     if a_offset + (H - 1) * a_head_stride + K + tail > a.shape[1] or out_offset + (H - 1) * out_head_stride + N + tail > out.shape[1]:
@@ -491,7 +495,7 @@ def head_product(a: torch.Tensor, a_offset: int, a_head_stride: int, w: torch.Te
         _dev(a, "a"), dtype_code(a.dtype), a.shape[1], int(a_offset), int(a_head_stride), _dev(w, "w"), dtype_code(w.dtype), N * K,
         _dev(out, "out"), dtype_code(out.dtype), out.shape[1], int(out_offset), int(out_head_stride), T, H, N, K, int(tail),
         _opt(freq, "freq", torch.float32), float(amplitude), 0 if positions is None else _dev(positions, "positions", torch.int32),
-        _stream()), "head_product")
+        _opt(gate, "gate", torch.float32), 0 if gate is None else gate.shape[1], int(gate_offset), _stream()), "head_product")
 
 
 def grouped_tile_rows() -> int:

@@ -45,7 +45,7 @@ _SIGNATURES = {
     "gi_attention_rows_set_mma": [c_int],
     "gi_attention_rows_set_pairs": [c_int],
     "gi_head_product": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong,
-                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p],
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     "gi_expert_product": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_longlong, c_int, c_longlong, c_int, c_int, c_float,
                           c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "gi_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -59,7 +59,7 @@ _SIGNATURES = {
     "gi_add_bias": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "gi_sigmoid_gate": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "gi_softcap": [c_void_p, c_longlong, c_float, c_void_p],
-    "gi_depth_mix": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
+    "gi_depth_mix": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
                      c_int, c_int, c_void_p],
     "gi_grouped_tile_rows": [],
     "gi_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,

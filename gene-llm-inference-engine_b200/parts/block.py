@@ -174,7 +174,8 @@ class ParallelBlock:
     result of the layer with slot j, x <- sum over j <= s of ``depth_weights``[j] R_j (weights: ``depth_weights`` [s + 1]);
     without a slot x <- fresh.
 
-    The stream stays 32-bit. Both sublayers add into ``y``, which is zero when they start; one kernel then forms fresh,
+    The stream stays 32-bit. Both sublayers add into ``y``, which is zero when they start; one kernel then forms fresh
+    (adding the bias of the feed-forward's last product, if it has one),
     keeps it in the step's history [tokens, slots, width], mixes, clears y and, when the next block is of this kind with a
     norm of a single weight, writes that block's normed input in the same pass (``ctx.carry``)."""
 
@@ -189,6 +190,9 @@ class ParallelBlock:
         if layer_spec.feed_forward is not None:
             self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward,
                                            sub_weights(weights, "feed_forward."), build)
+        # the bias of the feed-forward's last product is added by the kernel that ends the layer
+        leave = getattr(self.feed_forward, "leave_output_bias", None)
+        self.y_bias = leave() if leave is not None else None
         self.depth_weights = None
         if self.slot:
             if not (1 <= self.slot < self.slots):
@@ -230,7 +234,7 @@ class ParallelBlock:
                 self.feed_forward.forward(ctx, xn, y)
             kernels.depth_mix(x, y, self.mult, hist, self.slot, self.depth_weights, first=bool(first),
                               next_weight=nxt.mixer_norm.scalar if nxt else None, eps=nxt.mixer_norm.eps if nxt else 0.0,
-                              xn_out=xn if nxt else None)
+                              xn_out=xn if nxt else None, y_bias=self.y_bias)
 
         parts = [(self.mixer_norm, None), (self.mixer, run)] + ([(self.feed_forward, None)] if self.feed_forward is not None else [])
         key = _launch_key(ctx, *parts)

@@ -45,6 +45,13 @@ class SwiGLUFeedForward:
             self.b_gate_up = weights["b_gate_up"].reshape(-1).to(device=build.device, dtype=torch.float32).contiguous()
             self.b_down = weights["b_down"].reshape(-1).to(device=build.device, dtype=torch.float32).contiguous()
         self.dtype = build.compute_dtype
+        # a block that ends with a kernel of its own over the sublayers' sum may add ``b_down`` there (``leave_output_bias``)
+        self.output_bias_left = False
+
+    def leave_output_bias(self):
+        """The caller adds the last product's bias itself from now on; returns it (None without one)."""
+        self.output_bias_left = self.b_down is not None
+        return self.b_down
 
     @property
     def first_product(self):
@@ -69,7 +76,7 @@ class SwiGLUFeedForward:
             else:
                 kernels.gated_act(gu, h, self.activation, self.limit, self.b_gate_up)
         self.w_down.forward(h, x, accumulate=True)
-        if self.b_down is not None:
+        if self.b_down is not None and not self.output_bias_left:
             kernels.add_bias(x, self.b_down)
 
 

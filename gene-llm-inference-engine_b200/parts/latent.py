@@ -118,10 +118,6 @@ class LatentAttentionMixer:
         kernels.attention_rows_of_step(ctx, qa, cache, None, ol, tables, H, 1, kr + r, kr, self.scale, self.window, None, None,
                                        self.sink)
         att = ctx.scratch("att", (T, H * dv), self.dtype)
-        if self.output_gate:
-            heads = ctx.scratch("latent_heads", (T, H * dv), torch.float32)
-            kernels.head_product(ol, 0, kr, self.w_uv, heads, 0, dv)
-            kernels.sigmoid_gate(heads, down, self.gate_offset, att)
-        else:
-            kernels.head_product(ol, 0, kr, self.w_uv, att, 0, dv)
+        # the heads' value matrices; the output gate (its values lie in the first product's columns) in the same kernel
+        kernels.head_product(ol, 0, kr, self.w_uv, att, 0, dv, gate=down if self.output_gate else None, gate_offset=self.gate_offset)
         self.w_o.forward(att, x, accumulate=True, then=then)

@@ -206,7 +206,7 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]],
         t = t.detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"safetensors: cannot store dtype {t.dtype} ('{name}')")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""       # a single number has no dimension to view
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
         blobs.append(raw)
