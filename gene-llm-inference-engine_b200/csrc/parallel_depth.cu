@@ -58,37 +58,112 @@ softcap_kernel(float* __restrict__ z, float cap, float inv_cap, size_t total) {
         z[i] = cap * tanhf(z[i] * inv_cap);
 }
 
-constexpr int kDepthMaxPerThread = 16;      // a row of up to 256 * 16 values is kept in registers between the two passes
+constexpr int kDepthKept = 4;          // pieces of a row that a thread keeps in registers between the two passes
+constexpr int kDepthWeights = 64;      // mixing weights held in shared memory (more are read from global memory)
 
-// One block per row. The sum over the slots runs in slot order and the row's sum of squares in the order of the
-// RMSNorm kernels (a fixed strided assignment, a fixed xor tree, the warps in index order).
-template <typename TOut>
+template <int VEC> struct Piece { float v[VEC]; };
+template <int VEC> __device__ __forceinline__ Piece<VEC> load_piece(const float* p) {
+    Piece<VEC> r;
+    if constexpr (VEC == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; }
+    else r.v[0] = *p;
+    return r;
+}
+template <int VEC> __device__ __forceinline__ void store_piece(float* p, const Piece<VEC>& r) {
+    if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    else *p = r.v[0];
+}
+template <int VEC, typename TOut> __device__ __forceinline__ void store_piece_as(TOut* p, const Piece<VEC>& r) {
+    if constexpr (VEC == 4 && sizeof(TOut) == 2) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1]), hi = __floats2bfloat162_rn(r.v[2], r.v[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const uint32_t*>(&lo); raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = raw;
+    } else if constexpr (VEC == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    } else {
+        *p = from_float<TOut>(r.v[0]);
+    }
+}
+
+// One block per row; a thread takes pieces of VEC consecutive values (16-byte accesses when the width allows), piece
+// i of thread t at (i * 256 + t) * VEC. The sum over the slots runs in slot order; the row's sum of squares is each
+// thread's chain over its pieces, added by a fixed xor tree and then over the warps in index order: a row's result
+// depends on that row only. The first kDepthKept pieces of a thread stay in registers for the second pass.
+template <typename TOut, int VEC>
 __global__ void __launch_bounds__(256)
 depth_mix_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ y_bias, float m, float* __restrict__ hist, int slots, int slot,
                  const float* __restrict__ w, int first, const float* __restrict__ next_weight, float eps,
                  TOut* __restrict__ xn_out, int D) {
     pdl_prologue();
     __shared__ float warp_part[8];
+    __shared__ float s_w[kDepthWeights];
     const size_t row = static_cast<size_t>(blockIdx.x) * D;
     float* h = hist ? hist + static_cast<size_t>(blockIdx.x) * slots * D : nullptr;
-    float keep[kDepthMaxPerThread];
+    if (h) {
+        for (int j = threadIdx.x; j <= slot && j < kDepthWeights; j += 256) s_w[j] = w[j];
+        __syncthreads();
+    }
+    Piece<VEC> keep[kDepthKept];
     float ss = 0.f;
-    int n = 0;
-    for (int d = threadIdx.x; d < D; d += 256, ++n) {
-        const float x_old = x[row + d];
-        const float fresh = x_old + m * (y_bias ? y[row + d] + y_bias[d] : y[row + d]);
-        y[row + d] = 0.f;
-        float v = fresh;
-        if (h) {
-            if (first) h[d] = x_old;                       // slot 0: what the first layer read
-            h[static_cast<size_t>(slot) * D + d] = fresh;
-            v = 0.f;
-            for (int j = 0; j < slot; ++j) v = fmaf(w[j], first && j == 0 ? x_old : h[static_cast<size_t>(j) * D + d], v);
-            v = fmaf(w[slot], fresh, v);
+
+    // what a piece reads: the stream, the sublayers' sum (with the bias) and the weighted sum of the kept results before
+    // this layer's, in slot order (slot 0 is the stream itself while the history is still empty)
+    auto read = [&](int d, Piece<VEC>& x_old, Piece<VEC>& yy, Piece<VEC>& acc) {
+        x_old = load_piece<VEC>(x + row + d);
+        yy = load_piece<VEC>(y + row + d);
+        if (y_bias) {
+            const Piece<VEC> b = load_piece<VEC>(y_bias + d);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) yy.v[e] += b.v[e];
         }
-        x[row + d] = v;
-        if (n < kDepthMaxPerThread) keep[n] = v;
-        ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc.v[e] = 0.f;
+        if (h) {
+            for (int j = 0; j < slot; ++j) {
+                const Piece<VEC> hj = (first && j == 0) ? x_old : load_piece<VEC>(h + static_cast<size_t>(j) * D + d);
+                const float wj = j < kDepthWeights ? s_w[j] : w[j];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc.v[e] = fmaf(wj, hj.v[e], acc.v[e]);
+            }
+        }
+    };
+    // what it writes, after all of a thread's reads are on their way: the layer's result into its slot, the mixed stream, y = 0
+    auto write = [&](int d, const Piece<VEC>& x_old, const Piece<VEC>& yy, const Piece<VEC>& acc) -> Piece<VEC> {
+        Piece<VEC> fresh, v, zero;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { fresh.v[e] = x_old.v[e] + m * yy.v[e]; zero.v[e] = 0.f; }
+        store_piece<VEC>(y + row + d, zero);
+        v = fresh;
+        if (h) {
+            if (first) store_piece<VEC>(h + d, x_old);                  // slot 0: what the first layer read
+            store_piece<VEC>(h + static_cast<size_t>(slot) * D + d, fresh);
+            const float ws = slot < kDepthWeights ? s_w[slot] : w[slot];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v.v[e] = fmaf(ws, fresh.v[e], acc.v[e]);
+        }
+        store_piece<VEC>(x + row + d, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss = fmaf(v.v[e], v.v[e], ss);
+        return v;
+    };
+
+    {
+        Piece<VEC> xo[kDepthKept], yy[kDepthKept], acc[kDepthKept];
+#pragma unroll
+        for (int i = 0; i < kDepthKept; ++i) {
+            const int d = (i * 256 + threadIdx.x) * VEC;
+            if (d < D) read(d, xo[i], yy[i], acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < kDepthKept; ++i) {
+            const int d = (i * 256 + threadIdx.x) * VEC;
+            if (d < D) keep[i] = write(d, xo[i], yy[i], acc[i]);
+        }
+    }
+    for (int d = (kDepthKept * 256 + threadIdx.x) * VEC; d < D; d += 256 * VEC) {
+        Piece<VEC> xo, yy, acc;
+        read(d, xo, yy, acc);
+        write(d, xo, yy, acc);
     }
     if (xn_out == nullptr) return;
     ss = warp_sum(ss);
@@ -99,10 +174,21 @@ depth_mix_kernel(float* __restrict__ x, float* __restrict__ y, const float* __re
     for (int k = 0; k < 8; ++k) total += warp_part[k];
     const float scale = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
     const float g = next_weight ? next_weight[0] : 1.0f;
-    n = 0;
-    for (int d = threadIdx.x; d < D; d += 256, ++n) {
-        const float v = n < kDepthMaxPerThread ? keep[n] : x[row + d];
-        xn_out[row + d] = from_float<TOut>(g * (scale * v));
+#pragma unroll
+    for (int i = 0; i < kDepthKept; ++i) {
+        const int d = (i * 256 + threadIdx.x) * VEC;
+        if (d < D) {
+            Piece<VEC> o;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o.v[e] = g * (scale * keep[i].v[e]);
+            store_piece_as<VEC, TOut>(xn_out + row + d, o);
+        }
+    }
+    for (int d = (kDepthKept * 256 + threadIdx.x) * VEC; d < D; d += 256 * VEC) {
+        Piece<VEC> o = load_piece<VEC>(x + row + d);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o.v[e] = g * (scale * o.v[e]);
+        store_piece_as<VEC, TOut>(xn_out + row + d, o);
     }
 }
 
@@ -162,14 +248,21 @@ static int gi_depth_mix_impl(float* x, float* y, const float* y_bias, float m, f
     GI_REQUIRE(T > 0 && D > 0, "depth_mix: sizes must be positive");
     GI_REQUIRE(hist == nullptr || (w != nullptr && slot >= 1 && slot < slots), "depth_mix: slot %d lies outside the %d kept results", slot, slots);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (xn_dtype == kBF16)
-        launch_kernel((depth_mix_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
+    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec = D % 4 == 0 && aligned(x) && aligned(y) && aligned(hist) && aligned(y_bias) && aligned(xn_out);
+    GI_REQUIRE(xn_dtype == kBF16 || xn_dtype == kF32, "depth_mix: unsupported dtype code %d", xn_dtype);
+    if (xn_dtype == kBF16 && vec)
+        launch_kernel((depth_mix_kernel<__nv_bfloat16, 4>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
                       static_cast<__nv_bfloat16*>(xn_out), D);
-    else if (xn_dtype == kF32)
-        launch_kernel((depth_mix_kernel<float>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
+    else if (xn_dtype == kBF16)
+        launch_kernel((depth_mix_kernel<__nv_bfloat16, 1>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
+                      static_cast<__nv_bfloat16*>(xn_out), D);
+    else if (vec)
+        launch_kernel((depth_mix_kernel<float, 4>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
                       static_cast<float*>(xn_out), D);
     else
-        GI_REQUIRE(false, "depth_mix: unsupported dtype code %d", xn_dtype);
+        launch_kernel((depth_mix_kernel<float, 1>), dim3(T), dim3(256), 0, st, x, y, y_bias, m, hist, slots, slot, w, first, next_weight, eps,
+                      static_cast<float*>(xn_out), D);
     return check_launch("depth_mix");
 }
 
