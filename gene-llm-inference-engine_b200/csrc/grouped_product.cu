@@ -221,6 +221,13 @@ grouped_rows_kernel(const GroupedArgs p) {
 #pragma unroll
             for (int i = 0; i < kGrFew; ++i) { acc[r][i] = 0.f; if (GATED) acc_up[GATED ? r : 0][i] = 0.f; }
         }
+        // the output gate's values of the warp's 4 x kGrFew outputs, a lane each, asked for before the weights stream
+        float gate_z = 0.f;
+        if (p.gate != nullptr && lane < 4 * kGrFew) {
+            const int gr = lane / kGrFew, gi_ = lane % kGrFew;
+            if (gi_ < m_here && n_first + gr < p.N)
+                gate_z = p.gate[static_cast<size_t>(s_row[m0 + gi_]) * p.ldg + p.gate_off + static_cast<size_t>(g) * p.N + n_first + gr];
+        }
         for (int c = lane; c < pieces; c += 32) {
             float wv[4][8], uv[GATED ? 4 : 1][8];
 #pragma unroll
@@ -260,8 +267,8 @@ grouped_rows_kernel(const GroupedArgs p) {
                 if (i < m_here && n_first + r < p.N) {
                     float v = warp_sum(acc[r][i]);
                     if (GATED) v = gated_value(v, warp_sum(acc_up[GATED ? r : 0][i]), p.act, p.act_limit);
+                    if (p.gate != nullptr) v *= 1.0f / (1.0f + expf(-__shfl_sync(0xffffffffu, gate_z, r * kGrFew + i)));
                     if (lane == 0) {
-                        v = gp_gated(p, v, s_row[m0 + i], g, n_first + r);
                         const size_t o = static_cast<size_t>(s_row[m0 + i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n_first + r;
                         if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
                         else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);

@@ -577,3 +577,43 @@ def test_trace_replay_tool_and_command_line(tmp_path, tmp_path_factory):
         assert t == int(np.argmax(logits)) or float(logits.max() - logits[t]) < 1e-4
         tokens.append(t)
     assert len(out) == 9
+
+
+def _random_config(seed):
+    """A configuration drawn from a seed: sizes, layer order, feed-forward kinds and constants all differ from case to case."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([64, 72, 96, 160, 192, 256])
+    layers = []
+    for _ in range(r.randint(1, 7)):
+        kind = r.choice(["none", "dense", "moe", "moe", "moe"])
+        if kind == "none":
+            mlp = None
+        elif kind == "dense":
+            mlp = pc.dense(r.choice([40, 64, 136, 384, 100]))
+        else:
+            experts = r.randint(2, 16)
+            shared = (r.choice([8, 24, 64, 128]), r.choice([0.5, 1.5, 3.0])) if r.random() < 0.7 else None
+            mlp = pc.moe(r.choice([8, 24, 48, 96, 44]), r.choice([0.5, 1.0, 2.0, 7.0]), experts, r.randint(1, min(4, experts)), shared=shared)
+        layers.append(pc.layer(r.randint(1, 12), r.choice([8, 16, 32, 64, 96]), r.choice([8, 16, 40, 64, 80, 128]),
+                               r.choice([16, 32, 64, 96, 128, 192, 256]), r.choice([0.08, 0.125, 0.2, 0.3]), mlp))
+    return pc.model(width, r.randint(50, 600), 256, r.choice([1e-6, 1e-5, 1e-3]), r.choice([0.3, 0.5, 1.0, 1.4]),
+                    r.choice([5.0, 15.0, 30.0, 100.0]), layers)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_under_a_mixed_trace(seed, tmp_path):
+    config = _random_config(seed)
+    folder = pc.make_model_dir(config, 100 + seed, str(tmp_path / "m"), std=0.15)
+    cfg, w = pp.load(folder)
+    reqs = {f"r{i}": tc.random_tokens(n, config["vocab"], 700 + 10 * seed + i) for i, n in enumerate([130, 3, 61, 1, 200, 18])}
+    exact = {rid: pp.forward(cfg, w, toks)[0].numpy() for rid, toks in reqs.items()}
+    rounded = {rid: pp.forward(cfg, w, toks, pp.bf16)[0].numpy() for rid, toks in reqs.items()}
+    steps = tt.trace_mixed(reqs, seed=seed, tail=10)
+    for dtype in ("float32", "bfloat16"):
+        tol = 3e-5 if dtype == "float32" else 3.0 * max(tt.rel_err(rounded[r], exact[r]) for r in exact)
+        engine = _engine(folder, dtype, tt.max_tokens_of(steps, reqs, 16) // 16 + 4)
+        got = tt.run_in_process(engine, steps)
+        engine.check_status()
+        tt.compare(got, exact, tol, f"random configuration {seed} {dtype}")
+        assert all(g.pool.free_count == g.pool.n_pages for g in engine.cache.groups)
