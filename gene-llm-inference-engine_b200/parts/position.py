@@ -123,7 +123,7 @@ class RotaryOnDevice:
 
 @register_position_encoding("learned")
 class LearnedPosition:
-    """A learned vector per position, added to the embedding's output (not scaled); queries and keys are not rotated.
+    """A table of learned vectors, one per position, added as they are to the embedding's output; queries and keys are not rotated.
     Params: ``size`` (the model's width), ``positions`` (rows of the table: no position beyond it exists). Weights:
     ``table`` [positions, size]. The model calls ``add_to(ctx, x)`` once per step, after the embedding."""
 

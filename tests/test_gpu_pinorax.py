@@ -583,20 +583,20 @@ def _random_config(seed):
     """A configuration drawn from a seed: sizes, layer order, feed-forward kinds and constants all differ from case to case."""
     import random
     r = random.Random(seed)
-    width = r.choice([64, 72, 96, 160, 192, 256])
+    width = r.choice([64, 72, 96, 160, 176, 256])
     layers = []
     for _ in range(r.randint(1, 7)):
         kind = r.choice(["none", "dense", "moe", "moe", "moe"])
         if kind == "none":
             mlp = None
         elif kind == "dense":
-            mlp = pc.dense(r.choice([40, 64, 136, 384, 100]))
+            mlp = pc.dense(r.choice([40, 64, 136, 320, 100]))
         else:
             experts = r.randint(2, 16)
             shared = (r.choice([8, 24, 64, 128]), r.choice([0.5, 1.5, 3.0])) if r.random() < 0.7 else None
-            mlp = pc.moe(r.choice([8, 24, 48, 96, 44]), r.choice([0.5, 1.0, 2.0, 7.0]), experts, r.randint(1, min(4, experts)), shared=shared)
-        layers.append(pc.layer(r.randint(1, 12), r.choice([8, 16, 32, 64, 96]), r.choice([8, 16, 40, 64, 80, 128]),
-                               r.choice([16, 32, 64, 96, 128, 192, 256]), r.choice([0.08, 0.125, 0.2, 0.3]), mlp))
+            mlp = pc.moe(r.choice([8, 24, 48, 88, 44]), r.choice([0.5, 1.0, 2.0, 7.0]), experts, r.randint(1, min(4, experts)), shared=shared)
+        layers.append(pc.layer(r.randint(1, 12), r.choice([8, 16, 32, 64, 96]), r.choice([8, 16, 40, 64, 72, 128]),
+                               r.choice([16, 32, 64, 80, 128, 192, 256]), r.choice([0.08, 0.125, 0.2, 0.3]), mlp))
     return pc.model(width, r.randint(50, 600), 256, r.choice([1e-6, 1e-5, 1e-3]), r.choice([0.3, 0.5, 1.0, 1.4]),
                     r.choice([5.0, 15.0, 30.0, 100.0]), layers)
 
