@@ -930,6 +930,7 @@ struct TcPersistentParams {
     int gate_act;                // SwiGLU epilogue: what is applied to the gate (a GateAct code)
     float act_limit;             //   its limit (capped swish)
     const float* gate_up_bias;   //   optional: a bias on the gate channels and, up_row_offset values further, on the up channels
+    int bias_vec;                //   both halves of the bias start on 16-byte boundaries: whole groups of 8 channels take 16-byte loads
     int* status;
     int splits;                  // K is cut into this many ranges, each an accumulator tile of its own whose result is
     int kb_per_split;            //   stored split_rows rows further down in the output (a workspace; the ranges are
@@ -1251,18 +1252,31 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {          // 8 channels = 16 bytes of bfloat16 per step
                             uint32_t packed[4];
+                            float bg[8], bu[8];                   // a bias per gate and up channel (gate values first)
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) { bg[e] = 0.f; bu[e] = 0.f; }
+                            if (p.gate_up_bias) {
+                                const int gc = tile_q * (BLOCK_Q / 2) + ch + q4 * 8;
+                                if (p.bias_vec && gc + 8 <= p.rows_q) {
+                                    const float4* pg = reinterpret_cast<const float4*>(p.gate_up_bias + gc);
+                                    const float4* pu = reinterpret_cast<const float4*>(p.gate_up_bias + p.up_row_offset + gc);
+                                    const float4 g_lo = __ldg(pg), g_hi = __ldg(pg + 1), u_lo = __ldg(pu), u_hi = __ldg(pu + 1);
+                                    bg[0] = g_lo.x; bg[1] = g_lo.y; bg[2] = g_lo.z; bg[3] = g_lo.w;
+                                    bg[4] = g_hi.x; bg[5] = g_hi.y; bg[6] = g_hi.z; bg[7] = g_hi.w;
+                                    bu[0] = u_lo.x; bu[1] = u_lo.y; bu[2] = u_lo.z; bu[3] = u_lo.w;
+                                    bu[4] = u_hi.x; bu[5] = u_hi.y; bu[6] = u_hi.z; bu[7] = u_hi.w;
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        if (gc + e < p.rows_q) { bg[e] = __ldg(p.gate_up_bias + gc + e); bu[e] = __ldg(p.gate_up_bias + p.up_row_offset + gc + e); }
+                                }
+                            }
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const float g0 = __uint_as_float(r[q4 * 8 + 2 * e]), g1 = __uint_as_float(r[q4 * 8 + 2 * e + 1]);
                                 const float u0 = __uint_as_float(u[q4 * 8 + 2 * e]), u1 = __uint_as_float(u[q4 * 8 + 2 * e + 1]);
-                                float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
-                                if (p.gate_up_bias) {             // a bias per gate and up channel (gate values first)
-                                    const int gc = tile_q * (BLOCK_Q / 2) + ch + q4 * 8 + 2 * e;
-                                    if (gc < p.rows_q) { b0 = __ldg(p.gate_up_bias + gc); c0 = __ldg(p.gate_up_bias + p.up_row_offset + gc); }
-                                    if (gc + 1 < p.rows_q) { b1 = __ldg(p.gate_up_bias + gc + 1); c1 = __ldg(p.gate_up_bias + p.up_row_offset + gc + 1); }
-                                }
-                                const float h0 = gated_value(g0 + b0, u0 + c0, p.gate_act, p.act_limit);
-                                const float h1 = gated_value(g1 + b1, u1 + c1, p.gate_act, p.act_limit);
+                                const float h0 = gated_value(g0 + bg[2 * e], u0 + bu[2 * e], p.gate_act, p.act_limit);
+                                const float h1 = gated_value(g1 + bg[2 * e + 1], u1 + bu[2 * e + 1], p.gate_act, p.act_limit);
                                 __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
                                 packed[e] = *reinterpret_cast<uint32_t*>(&hb);
                             }
@@ -1745,6 +1759,7 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     const int rows_per_tile_p = pair ? 2 * kBlockP : kBlockP;
     p.up_row_offset = N;
     p.gate_act = gate_act; p.act_limit = act_limit; p.gate_up_bias = gate_up_bias;
+    p.bias_vec = gate_up_bias != nullptr && reinterpret_cast<uintptr_t>(gate_up_bias) % 16 == 0 && N % 4 == 0;
     p.status = static_cast<int*>(status);
     const int total_kb = (K + kBlockK - 1) / kBlockK;
     p.splits = 1; p.kb_per_split = total_kb; p.split_rows = 0;
