@@ -3,9 +3,10 @@ from .llama import LlamaConfig, RopeScaling, parse_rope_scaling
 from .nipadra import NipadraConfig
 from .gekupel import GekupelConfig
 from .pinorax import PinoraxConfig
+from .fovezen import FovezenConfig
 from .registry import (Architecture, known_architectures, parse_config, register_architecture,
                        resolve_architecture)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "LlamaConfig", "NipadraConfig", "GekupelConfig", "PinoraxConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "LlamaConfig", "NipadraConfig", "GekupelConfig", "PinoraxConfig", "FovezenConfig",
            "RopeScaling", "parse_rope_scaling", "Architecture", "known_architectures", "parse_config",
            "register_architecture", "resolve_architecture"]

@@ -8,6 +8,7 @@
 //   chunk    c > 0: only keys of the query's own block of c positions counted from 0, floor(j / c) = floor(P / c)
 //   slopes   [H] or null: slope_h * (P - j) is taken off the score of key j (a bias that grows with the distance)
 //   sinks    [H] or null: the softmax's denominator also holds exp(sinks_h), a term without key or value
+//   softcap  c > 0: the scaled score s becomes c tanh(s / c) before bias and softmax
 //   values   a width ``vd`` of their own; they may lie in pages of their own or be the first vd columns of the key
 //            rows (``v_row`` is the length of the rows they lie in), which serves attention over a shared latent whose
 //            keys are [latent, rotated part] and whose values are the latent itself
@@ -35,12 +36,14 @@ struct RowsArgs {
     void* out; int out_is_f32; int ldo;            // [T, ldo], head h at column h * vd
     const int* row_req; const int* positions; const int* block_tables; int table_stride;
     int H, Hkv, hd, vd, v_row, page_size;
-    float scale; int window, chunk;
+    float scale; float softcap; int window, chunk;
     const float* slopes; const float* sinks;
     int heads_per_block;                           // query heads of one key/value head that a block takes
     int ks;                                        // row length of the key tile in shared memory (elements)
     int alias;                                     // the values are the first vd columns of the key rows
 };
+
+__device__ __forceinline__ float capped(float score, float cap) { return cap > 0.f ? cap * tanhf(score / cap) : score; }
 
 // HPW: query heads per warp; VI: value dimensions per lane (vd <= 32 * VI).
 template <typename T, int HPW, int VI>
@@ -134,7 +137,7 @@ attention_rows_kernel(const RowsArgs a) {
         float p[HPW];
 #pragma unroll
         for (int hh = 0; hh < HPW; ++hh) {
-            const float score = valid ? s[hh] * a.scale - slope[hh] * static_cast<float>(pos - (base + lane)) : -INFINITY;
+            const float score = valid ? capped(s[hh] * a.scale, a.softcap) - slope[hh] * static_cast<float>(pos - (base + lane)) : -INFINITY;
             const float m_new = fmaxf(m[hh], warp_max(score));          // finite: a tile always holds a visible key
             p[hh] = valid ? expf(score - m_new) : 0.f;
             const float corr = (m[hh] == -INFINITY) ? 0.f : expf(m[hh] - m_new);
@@ -429,7 +432,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
                 const int h = e >> 1, col = nt * 8 + 2 * tq + (e & 1);
                 float v = s[nt][e];
                 const int key = base + col;
-                v = (key >= lo_r[h] && key <= pos_r[h]) ? v * a.scale - slope[h] * static_cast<float>(pos_r[h] - key) : -INFINITY;
+                v = (key >= lo_r[h] && key <= pos_r[h]) ? capped(v * a.scale, a.softcap) - slope[h] * static_cast<float>(pos_r[h] - key) : -INFINITY;
                 s[nt][e] = v;
                 tile_max[h] = fmaxf(tile_max[h], v);
             }
@@ -648,7 +651,7 @@ extern "C" int gi_attention_rows_tile_tokens(int H, int Hkv, int hd, int vd, int
 static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                                  void* out, int out_dtype, int ldo, const int* row_req, const int* positions,
                                  const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int vd, int v_row,
-                                 int values_in_keys, int page_size, float scale, int window, int chunk, const float* slopes,
+                                 int values_in_keys, int page_size, float scale, float softcap, int window, int chunk, const float* slopes,
                                  const float* sinks, const int* tile_list, int list_kind, int n_tiles, int splits, float* workspace,
                                  long long workspace_floats, void* stream) {
     if (T == 0 || (list_kind != 0 && n_tiles == 0)) return 0;
@@ -668,7 +671,7 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
     a.out = out; a.out_is_f32 = out_dtype == kF32; a.ldo = ldo;
     a.row_req = row_req; a.positions = positions; a.block_tables = block_tables; a.table_stride = table_stride;
     a.H = H; a.Hkv = Hkv; a.hd = hd; a.vd = vd; a.v_row = v_row; a.page_size = page_size;
-    a.scale = scale; a.window = window; a.chunk = chunk; a.slopes = slopes; a.sinks = sinks;
+    a.scale = scale; a.softcap = softcap; a.window = window; a.chunk = chunk; a.slopes = slopes; a.sinks = sinks;
     a.alias = values_in_keys ? 1 : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // bfloat16 cache and sizes in whole MMA tiles: the tensor-core form (tiles of rows from the caller's list, or a row each)
@@ -719,10 +722,10 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
 extern "C" int gi_attention_rows(const void* q, int q_dtype, int ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                                  void* out, int out_dtype, int ldo, const int* row_req, const int* positions,
                                  const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int vd, int v_row,
-                                 int values_in_keys, int page_size, float scale, int window, int chunk, const float* slopes,
+                                 int values_in_keys, int page_size, float scale, float softcap, int window, int chunk, const float* slopes,
                                  const float* sinks, const int* tile_list, int list_kind, int n_tiles, int splits, float* workspace,
                                  long long workspace_floats, void* stream) {
     return gi::dispatch(gi_attention_rows_impl, q, q_dtype, ldq, k_cache, v_cache, cache_dtype, out, out_dtype, ldo, row_req,
-                        positions, block_tables, table_stride, T, H, Hkv, hd, vd, v_row, values_in_keys, page_size, scale, window,
+                        positions, block_tables, table_stride, T, H, Hkv, hd, vd, v_row, values_in_keys, page_size, scale, softcap, window,
                         chunk, slopes, sinks, tile_list, list_kind, n_tiles, splits, workspace, workspace_floats, stream);
 }

@@ -3,10 +3,11 @@
 //     S_t = a_t S_(t-1) + b_t k_t v_t^T        (S: dk x dv per head, 32-bit, in the request's state slot)
 //     o_t = S_t^T q_t + D v_t
 //
-// with its two families of decay: a constant a per head and b = 1 (linear attention with decay), and
+// with its families of decay: a constant a per head and b = 1 (linear attention with decay);
 // a_t = exp(-exp(A_log) dt_t), b_t = dt_t with dt_t = softplus(raw_t + bias) per head and token (state-space
-// duality). Around it: the short causal convolution over a request's tokens whose last inputs are state too,
-// and the unit-RMS norm over groups of channels with a gate before (SiLU) or after (sigmoid) the norm.
+// duality); and a factor of its own for every row of S, S_t = diag(alpha_t) S_(t-1) + k_t v_t^T with
+// alpha_t = sigmoid(z_t)^(1/tau) per head, key channel and token (gated linear attention). Around it: the short causal convolution over a request's tokens whose last inputs are state too (with or without a bias
+// and SiLU), and the unit-RMS norm over groups of channels with a gate before (SiLU) or after (sigmoid or SiLU) the norm.
 //
 // A step's rows are segments (one per request: seg_start, seg_len, state_slots as the step's descriptor holds
 // them on the device). Tokens of a segment are taken in order, one after the other, by the same threads with the
@@ -20,13 +21,13 @@ __device__ __forceinline__ float silu_f(float z) { return z * (1.0f / (1.0f + ex
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // ---------------------------------------------------------------------------------- causal convolution
-// out[t, c] = silu(bias[c] + sum_j w[c, j] * u(t - (taps-1) + j, c)); u before the segment's first row is the
+// out[t, c] = act(bias[c] + sum_j w[c, j] * u(t - (taps-1) + j, c)), act SiLU or nothing, bias optional; u before the segment's first row is the
 // request's conv state [taps-1, C] (oldest first; zeros for a new request), u before the sequence is zero.
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const float* __restrict__ in, int ld, int in_off, const float* __restrict__ weight,
                    const float* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
                    const int* __restrict__ row_req, const int* __restrict__ seg_start,
-                   const int* __restrict__ state_slots, float* __restrict__ out, int C, int taps, int T) {
+                   const int* __restrict__ state_slots, float* __restrict__ out, int C, int taps, int T, int act) {
     pdl_prologue();
     const int c = blockIdx.x * 256 + threadIdx.x;
     const int t = blockIdx.y;
@@ -34,7 +35,7 @@ causal_conv_kernel(const float* __restrict__ in, int ld, int in_off, const float
     const int r = row_req[t];
     const int rel = t - seg_start[r];
     const float* st = state + static_cast<long long>(state_slots[r]) * slot_stride;
-    float acc = bias[c];
+    float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;                 // how many tokens before t
         float u;
@@ -42,7 +43,7 @@ causal_conv_kernel(const float* __restrict__ in, int ld, int in_off, const float
         else u = st[static_cast<size_t>(taps - 1 + rel - back) * C + c];
         acc = fmaf(weight[static_cast<size_t>(c) * taps + j], u, acc);
     }
-    out[static_cast<size_t>(t) * C + c] = silu_f(acc);
+    out[static_cast<size_t>(t) * C + c] = act ? silu_f(acc) : acc;
 }
 
 // The state after the step: the last taps-1 inputs of each segment (older ones from the old state).
@@ -87,13 +88,19 @@ struct ScanArgs {
     const float* decay;                                   // [H] constant decays, or null for the dt form
     const float* dt_raw; int ld_dt, dt_off;               // [T, ld_dt] at dt_off + h
     const float* dt_bias; const float* a_log; const float* skip;      // [H] each; skip may be null
+    const float* gate_raw; int ld_gate, gate_off;         // [T, ld_gate] at gate_off + h * dk + i: z of the per-row decay, or null
+    const float* gate_bias; float inv_tau;                // [H * dk] added to z (may be null); alpha = sigmoid(z)^inv_tau
+    float q_scale;                                        // a constant on the queries
     float* state; long long slot_stride; long long state_off;          // per slot: [H, dk, dv] at state_off
     const int* seg_start; const int* seg_len; const int* state_slots;
     float* out;                                           // [T, H * dv]
     int part_len, max_parts;                              // kParts: tokens per part, parts per request in the grid
     float* ws_state;                                      // [parts of the step, H, dk, dv]
-    float* ws_decay;                                      // [T, H]
+    float* ws_decay;                                      // [T, H]; with per-row decays [T, H, dk]
 };
+
+// sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
+__device__ __forceinline__ float row_decay(float z, float inv_tau) { return expf(-softplus_f(-z) * inv_tau); }
 
 // Where request r's parts start among the step's parts: the parts of the requests before it.
 __device__ __forceinline__ int parts_before(const ScanArgs& p, int r) {
@@ -102,7 +109,7 @@ __device__ __forceinline__ int parts_before(const ScanArgs& p, int r) {
     return base;
 }
 
-template <int kDk, int kRT, bool kParts>
+template <int kDk, int kRT, bool kParts, bool kRowDecay>
 __global__ void __launch_bounds__(kDk / kRT * 8)
 linear_scan_kernel(const ScanArgs p) {
     pdl_prologue();
@@ -120,6 +127,7 @@ linear_scan_kernel(const ScanArgs p) {
     __shared__ __align__(16) float s_v[kChunk][kScanCols];
     __shared__ __align__(16) float s_o[kChunk][kGroups][kScanCols];
     __shared__ float s_a[kChunk], s_b[kChunk];
+    __shared__ __align__(16) float s_av[kRowDecay ? kChunk : 1][kRowDecay ? kDk : 4];      // per-row decays of the staged tokens
     const int tile = blockIdx.x, h = blockIdx.y;
     const int r = kParts ? blockIdx.z / p.max_parts : blockIdx.z;
     const int part_idx = kParts ? blockIdx.z % p.max_parts : 0;
@@ -147,11 +155,16 @@ linear_scan_kernel(const ScanArgs p) {
     }
     const float skip = p.skip ? p.skip[h] : 0.f;
     const float a_const = p.decay ? p.decay[h] : 0.f;
-    const float neg_rate = p.decay ? 0.f : -expf(p.a_log[h]);
-    const float bias = p.decay ? 0.f : p.dt_bias[h];
+    const bool stepped = !kRowDecay && !p.decay;         // a and b from the step size
+    const float neg_rate = stepped ? -expf(p.a_log[h]) : 0.f;
+    const float bias = stepped ? p.dt_bias[h] : 0.f;
     float cum = 1.f;                                      // thread 0: product of the decays since the part's start
+    constexpr int kCumPerThread = (kDk + kThreads - 1) / kThreads;
+    float cumv[kCumPerThread];                            // per-row decays: the products of rows threadIdx.x + u * kThreads
+#pragma unroll
+    for (int u = 0; u < kCumPerThread; ++u) cumv[u] = 1.f;
     // the loads of a chunk are requested while the chunk before it is worked on
-    float qv[kPerThread], kv[kPerThread], vv[kVPerThread], dt_raw = 0.f;
+    float qv[kPerThread], kv[kPerThread], zv[kRowDecay ? kPerThread : 1], vv[kVPerThread], dt_raw = 0.f;
     auto request = [&](int c0) {
         const int m = min(kChunk, n - c0);
 #pragma unroll
@@ -162,6 +175,8 @@ linear_scan_kernel(const ScanArgs p) {
             const bool in = tt < m && i < p.dk;
             qv[u] = in ? p.q[t * p.ld_q + p.q_off + g * p.dk + i] : 0.f;
             kv[u] = in ? p.k[t * p.ld_k + p.k_off + g * p.dk + i] : 0.f;
+            if (kRowDecay)
+                zv[u] = in ? p.gate_raw[t * p.ld_gate + p.gate_off + h * p.dk + i] + (p.gate_bias ? p.gate_bias[h * p.dk + i] : 0.f) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < kVPerThread; ++u) {
@@ -169,7 +184,7 @@ linear_scan_kernel(const ScanArgs p) {
             const int tt = e / kScanCols, jj = tile * kScanCols + e % kScanCols;
             vv[u] = (tt < m && jj < p.dv) ? p.v[static_cast<size_t>(s0 + c0 + tt) * p.ld_v + p.v_off + h * p.dv + jj] : 0.f;
         }
-        if (!p.decay && threadIdx.x < m)
+        if (!kRowDecay && !p.decay && threadIdx.x < m)
             dt_raw = p.dt_raw[static_cast<size_t>(s0 + c0 + threadIdx.x) * p.ld_dt + p.dt_off + h];
     };
     request(0);
@@ -179,8 +194,9 @@ linear_scan_kernel(const ScanArgs p) {
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             const int e = threadIdx.x + u * kThreads;
-            s_q[e / kDk][e % kDk] = p.act ? silu_f(qv[u]) : qv[u];
+            s_q[e / kDk][e % kDk] = (p.act ? silu_f(qv[u]) : qv[u]) * p.q_scale;
             s_k[e / kDk][e % kDk] = p.act ? silu_f(kv[u]) : kv[u];
+            if (kRowDecay) s_av[e / kDk][e % kDk] = (e / kDk < m && e % kDk < p.dk) ? row_decay(zv[u], p.inv_tau) : 1.f;
         }
 #pragma unroll
         for (int u = 0; u < kVPerThread; ++u) {
@@ -188,7 +204,10 @@ linear_scan_kernel(const ScanArgs p) {
             s_v[e / kScanCols][e % kScanCols] = p.act ? silu_f(vv[u]) : vv[u];
         }
         if (threadIdx.x < m) {
-            if (p.decay) {
+            if (kRowDecay) {
+                s_a[threadIdx.x] = 1.f;
+                s_b[threadIdx.x] = 1.f;
+            } else if (p.decay) {
                 s_a[threadIdx.x] = a_const;
                 s_b[threadIdx.x] = 1.f;
             } else {
@@ -199,10 +218,22 @@ linear_scan_kernel(const ScanArgs p) {
         }
         __syncthreads();
         if (c0 + kChunk < n) request(c0 + kChunk);
-        if (kParts && tile == 0 && threadIdx.x == 0) {
+        if (kParts && !kRowDecay && tile == 0 && threadIdx.x == 0) {
             for (int tt = 0; tt < m; ++tt) {
                 cum *= s_a[tt];
                 p.ws_decay[static_cast<size_t>(s0 + c0 + tt) * p.H + h] = cum;
+            }
+        }
+        if (kParts && kRowDecay && tile == 0) {
+#pragma unroll
+            for (int u = 0; u < kCumPerThread; ++u) {
+                const int i = threadIdx.x + u * kThreads;
+                if (i < p.dk) {
+                    for (int tt = 0; tt < m; ++tt) {
+                        cumv[u] *= s_av[tt][i];
+                        p.ws_decay[(static_cast<size_t>(s0 + c0 + tt) * p.H + h) * p.dk + i] = cumv[u];
+                    }
+                }
             }
         }
         for (int tt = 0; tt < m; ++tt) {
@@ -216,11 +247,16 @@ linear_scan_kernel(const ScanArgs p) {
             for (int i4 = 0; i4 < kRT / 4; ++i4) {
                 const float4 kk = k4[i4], qq = q4[i4];
                 const float kr[4] = {kk.x, kk.y, kk.z, kk.w}, qr[4] = {qq.x, qq.y, qq.z, qq.w};
+                float ar[4] = {a, a, a, a};
+                if (kRowDecay) {
+                    const float4 aa = reinterpret_cast<const float4*>(&s_av[tt][rg * kRT])[i4];
+                    ar[0] = aa.x; ar[1] = aa.y; ar[2] = aa.z; ar[3] = aa.w;
+                }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        s[4 * i4 + u][c] = fmaf(a, s[4 * i4 + u][c], kr[u] * bv[c]);
+                        s[4 * i4 + u][c] = fmaf(ar[u], s[4 * i4 + u][c], kr[u] * bv[c]);
                         o[c] = fmaf(s[4 * i4 + u][c], qr[u], o[c]);
                     }
                 }
@@ -270,7 +306,8 @@ scan_link_kernel(const ScanArgs p) {
             const bool in = q < parts;
             const int last = s0 + min((q + 1) * p.part_len, n) - 1;
             U[u] = in ? ws[static_cast<size_t>(q) * p.H * per_head + e] : 0.f;
-            A[u] = in ? p.ws_decay[static_cast<size_t>(last) * p.H + h] : 1.f;
+            A[u] = !in ? 1.f : p.gate_raw ? p.ws_decay[(static_cast<size_t>(last) * p.H + h) * p.dk + (e % per_head) / p.dv]
+                                          : p.ws_decay[static_cast<size_t>(last) * p.H + h];
         }
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
@@ -308,14 +345,17 @@ scan_apply_kernel(const ScanArgs p) {
     }
     // the queries of a chunk are requested while the chunk before it is worked on
     constexpr int kPerThread = kChunk * kDk / 128;
-    float qv[kPerThread];
+    float qv[kPerThread], cv[kPerThread];
     auto request = [&](int c0) {
         const int m = min(kChunk, n - c0);
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             const int e = threadIdx.x + u * 128;
             const int tt = e / kDk, i = e % kDk;
-            qv[u] = (tt < m && i < p.dk) ? p.q[static_cast<size_t>(s0 + c0 + tt) * p.ld_q + p.q_off + g * p.dk + i] : 0.f;
+            const bool in = tt < m && i < p.dk;
+            qv[u] = in ? p.q[static_cast<size_t>(s0 + c0 + tt) * p.ld_q + p.q_off + g * p.dk + i] : 0.f;
+            // per-row decays: the product since the part's start scales the query's own channel
+            cv[u] = (in && p.gate_raw) ? p.ws_decay[(static_cast<size_t>(s0 + c0 + tt) * p.H + h) * p.dk + i] : 1.f;
         }
     };
     request(0);
@@ -325,7 +365,7 @@ scan_apply_kernel(const ScanArgs p) {
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             const int e = threadIdx.x + u * 128;
-            s_qT[e % kDk][e / kDk] = p.act ? silu_f(qv[u]) : qv[u];
+            s_qT[e % kDk][e / kDk] = (p.act ? silu_f(qv[u]) : qv[u]) * p.q_scale * cv[u];
         }
         __syncthreads();
         if (c0 + kChunk < n) request(c0 + kChunk);
@@ -337,7 +377,7 @@ scan_apply_kernel(const ScanArgs p) {
             const bool in = tt < m && j < p.dv;
             const size_t t = static_cast<size_t>(s0 + c0 + (in ? tt : 0));
             old[u] = in ? p.out[t * p.H * p.dv + h * p.dv + j] : 0.f;
-            dec[u] = in ? p.ws_decay[t * p.H + h] : 0.f;
+            dec[u] = !in ? 0.f : p.gate_raw ? 1.f : p.ws_decay[t * p.H + h];
         }
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         if (warp * 4 < kChunk)
@@ -360,7 +400,8 @@ scan_apply_kernel(const ScanArgs p) {
 }
 
 // ---------------------------------------------------------------------------------- gated group norm
-// One block per (token, group). mode 0: out = w * unit_rms(y) * sigmoid(gate); mode 1: out = w * unit_rms(y * silu(gate)).
+// One block per (token, group). mode 0: out = w * unit_rms(y) * sigmoid(gate); mode 1: out = w * unit_rms(y * silu(gate));
+// mode 2: out = w * unit_rms(y) * silu(gate).
 // Groups of at most 4096 channels in 16-byte pieces (kVec) are read once and kept in registers between the sum
 // and the scaling; the sum's order (a fixed strided assignment, a fixed xor tree, the warps in index order) is
 // the same in both forms.
@@ -418,6 +459,8 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ g
             if (mode == 0) {
                 r[0] *= 1.0f / (1.0f + expf(-gk[k].x)); r[1] *= 1.0f / (1.0f + expf(-gk[k].y));
                 r[2] *= 1.0f / (1.0f + expf(-gk[k].z)); r[3] *= 1.0f / (1.0f + expf(-gk[k].w));
+            } else if (mode == 2) {
+                r[0] *= silu_f(gk[k].x); r[1] *= silu_f(gk[k].y); r[2] *= silu_f(gk[k].z); r[3] *= silu_f(gk[k].w);
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c) o[4 * i + c] = from_float<TOut>(r[c] * out_scale);
@@ -426,6 +469,7 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ g
         for (int d = threadIdx.x; d < n; d += 256) {
             float v;
             if (mode == 1) v = w[d] * (scale * (yr[d] * silu_f(gr[d])));
+            else if (mode == 2) v = w[d] * (scale * yr[d]) * silu_f(gr[d]);
             else v = w[d] * (scale * yr[d]) * (1.0f / (1.0f + expf(-gr[d])));
             o[d] = from_float<TOut>(v * out_scale);
         }
@@ -439,7 +483,7 @@ using namespace gi;
 static int gi_causal_conv_impl(const float* in, int ld, int in_off, const float* weight, const float* bias, float* state,
                                long long slot_stride, long long state_off, const int* row_req, const int* seg_start,
                                const int* seg_len, const int* state_slots, float* out, int C, int taps, int T, int R,
-                               void* stream) {
+                               int act, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && R > 0 && C > 0, "causal_conv: sizes must be positive");
     GI_REQUIRE(taps >= 1 && taps <= 17, "causal_conv: %d taps are not supported (1 to 17)", taps);
@@ -448,7 +492,7 @@ static int gi_causal_conv_impl(const float* in, int ld, int in_off, const float*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const unsigned cb = (C + 255) / 256;
     launch_kernel((causal_conv_kernel), dim3(cb, T), dim3(256), 0, st, in, ld, in_off, weight, bias,
-                  static_cast<const float*>(state + state_off), slot_stride, row_req, seg_start, state_slots, out, C, taps, T);
+                  static_cast<const float*>(state + state_off), slot_stride, row_req, seg_start, state_slots, out, C, taps, T, act);
     if (taps > 1)
         launch_kernel((conv_state_update_kernel), dim3(cb, R), dim3(256), 0, st, in, ld, in_off, state + state_off, slot_stride,
                       seg_start, seg_len, state_slots, C, taps);
@@ -459,11 +503,14 @@ template <int kDk, int kRT>
 static void launch_scan(const ScanArgs& a, int R, cudaStream_t st) {
     const unsigned tiles = (a.dv + kScanCols - 1) / kScanCols;
     constexpr int kThreads = kDk / kRT * 8;
+    const bool rows = a.gate_raw != nullptr;
     if (a.part_len == 0) {
-        launch_kernel((linear_scan_kernel<kDk, kRT, false>), dim3(tiles, a.H, R), dim3(kThreads), 0, st, a);
+        if (rows) launch_kernel((linear_scan_kernel<kDk, kRT, false, true>), dim3(tiles, a.H, R), dim3(kThreads), 0, st, a);
+        else launch_kernel((linear_scan_kernel<kDk, kRT, false, false>), dim3(tiles, a.H, R), dim3(kThreads), 0, st, a);
         return;
     }
-    launch_kernel((linear_scan_kernel<kDk, kRT, true>), dim3(tiles, a.H, R * a.max_parts), dim3(kThreads), 0, st, a);
+    if (rows) launch_kernel((linear_scan_kernel<kDk, kRT, true, true>), dim3(tiles, a.H, R * a.max_parts), dim3(kThreads), 0, st, a);
+    else launch_kernel((linear_scan_kernel<kDk, kRT, true, false>), dim3(tiles, a.H, R * a.max_parts), dim3(kThreads), 0, st, a);
     const size_t elements = static_cast<size_t>(a.H) * a.dk * a.dv;
     launch_kernel((scan_link_kernel), dim3(static_cast<unsigned>((elements + 255) / 256), R), dim3(256), 0, st, a);
     launch_kernel((scan_apply_kernel<kDk>), dim3(tiles, a.H, R * a.max_parts), dim3(128), 0, st, a);
@@ -475,20 +522,23 @@ static void launch_scan(const ScanArgs& a, int R, cudaStream_t st) {
 static int gi_linear_scan_impl(const float* q, int ld_q, int q_off, const float* k, int ld_k, int k_off, const float* v,
                                int ld_v, int v_off, int H, int group, int dk, int dv, int act, const float* decay,
                                const float* dt_raw, int ld_dt, int dt_off, const float* dt_bias, const float* a_log,
-                               const float* skip, float* state, long long slot_stride, long long state_off,
+                               const float* skip, const float* gate_raw, int ld_gate, int gate_off, const float* gate_bias,
+                               float inv_tau, float q_scale, float* state, long long slot_stride, long long state_off,
                                const int* seg_start, const int* seg_len, const int* state_slots, float* out, int R,
                                int part_len, int max_parts, float* ws_state, float* ws_decay, void* stream) {
     if (R == 0) return 0;
     GI_REQUIRE(R > 0 && H > 0 && dk > 0 && dv > 0 && group > 0, "linear_scan: sizes must be positive");
     GI_REQUIRE(H % group == 0, "linear_scan: %d heads are not a multiple of the group size %d", H, group);
     GI_REQUIRE(dk <= 256, "linear_scan: %d state rows per head exceed 256", dk);
-    GI_REQUIRE(decay != nullptr || (dt_raw != nullptr && dt_bias != nullptr && a_log != nullptr),
-               "linear_scan: neither constant decays nor step sizes are given");
+    GI_REQUIRE(decay != nullptr || gate_raw != nullptr || (dt_raw != nullptr && dt_bias != nullptr && a_log != nullptr),
+               "linear_scan: neither constant decays nor step sizes nor per-row decays are given");
+    GI_REQUIRE(gate_raw == nullptr || (group == 1 && gate_off >= 0 && gate_off + H * dk <= ld_gate),
+               "linear_scan: per-row decays need a key head per head and their columns inside a row of %d", ld_gate);
     GI_REQUIRE(part_len == 0 || (part_len > 0 && max_parts > 0 && ws_state != nullptr && ws_decay != nullptr),
                "linear_scan: parts need their length, their number and both workspaces");
     GI_REQUIRE(static_cast<long long>(R) * (part_len ? max_parts : 1) <= 65535 && H <= 65535, "linear_scan: the grid limit 65535 is exceeded");
     ScanArgs a{q, k, v, ld_q, ld_k, ld_v, q_off, k_off, v_off, H, group, dk, dv, act, decay, dt_raw, ld_dt, dt_off, dt_bias,
-               a_log, skip, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, part_len, max_parts, ws_state,
+               a_log, skip, gate_raw, ld_gate, gate_off, gate_bias, inv_tau, q_scale, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, part_len, max_parts, ws_state,
                ws_decay};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // (padded state rows, rows per thread)
@@ -505,7 +555,7 @@ static int gi_gated_group_norm_impl(const float* y, const float* gate, int ld_ga
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && W > 0 && groups > 0 && W % groups == 0, "gated_group_norm: %d channels do not split into %d groups", W, groups);
     GI_REQUIRE(T <= 2147483647 && groups <= 65535, "gated_group_norm: the grid limit is exceeded");
-    GI_REQUIRE(mode == 0 || mode == 1, "gated_group_norm: unknown mode %d", mode);
+    GI_REQUIRE(mode >= 0 && mode <= 2, "gated_group_norm: unknown mode %d", mode);
     GI_REQUIRE(gate_off >= 0 && gate_off + W <= ld_gate, "gated_group_norm: the gate lies outside its row of %d", ld_gate);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int n = W / groups;
@@ -524,12 +574,12 @@ static int gi_gated_group_norm_impl(const float* y, const float* gate, int ld_ga
     return check_launch("gated_group_norm");
 }
 
-extern "C" int gi_causal_conv(const float* in, int ld, int in_off, const float* weight, const float* bias, float* state, long long slot_stride, long long state_off, const int* row_req, const int* seg_start, const int* seg_len, const int* state_slots, float* out, int C, int taps, int T, int R, void* stream) {
-    return gi::dispatch(gi_causal_conv_impl, in, ld, in_off, weight, bias, state, slot_stride, state_off, row_req, seg_start, seg_len, state_slots, out, C, taps, T, R, stream);
+extern "C" int gi_causal_conv(const float* in, int ld, int in_off, const float* weight, const float* bias, float* state, long long slot_stride, long long state_off, const int* row_req, const int* seg_start, const int* seg_len, const int* state_slots, float* out, int C, int taps, int T, int R, int act, void* stream) {
+    return gi::dispatch(gi_causal_conv_impl, in, ld, in_off, weight, bias, state, slot_stride, state_off, row_req, seg_start, seg_len, state_slots, out, C, taps, T, R, act, stream);
 }
 
-extern "C" int gi_linear_scan(const float* q, int ld_q, int q_off, const float* k, int ld_k, int k_off, const float* v, int ld_v, int v_off, int H, int group, int dk, int dv, int act, const float* decay, const float* dt_raw, int ld_dt, int dt_off, const float* dt_bias, const float* a_log, const float* skip, float* state, long long slot_stride, long long state_off, const int* seg_start, const int* seg_len, const int* state_slots, float* out, int R, int part_len, int max_parts, float* ws_state, float* ws_decay, void* stream) {
-    return gi::dispatch(gi_linear_scan_impl, q, ld_q, q_off, k, ld_k, k_off, v, ld_v, v_off, H, group, dk, dv, act, decay, dt_raw, ld_dt, dt_off, dt_bias, a_log, skip, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, R, part_len, max_parts, ws_state, ws_decay, stream);
+extern "C" int gi_linear_scan(const float* q, int ld_q, int q_off, const float* k, int ld_k, int k_off, const float* v, int ld_v, int v_off, int H, int group, int dk, int dv, int act, const float* decay, const float* dt_raw, int ld_dt, int dt_off, const float* dt_bias, const float* a_log, const float* skip, const float* gate_raw, int ld_gate, int gate_off, const float* gate_bias, float inv_tau, float q_scale, float* state, long long slot_stride, long long state_off, const int* seg_start, const int* seg_len, const int* state_slots, float* out, int R, int part_len, int max_parts, float* ws_state, float* ws_decay, void* stream) {
+    return gi::dispatch(gi_linear_scan_impl, q, ld_q, q_off, k, ld_k, k_off, v, ld_v, v_off, H, group, dk, dv, act, decay, dt_raw, ld_dt, dt_off, dt_bias, a_log, skip, gate_raw, ld_gate, gate_off, gate_bias, inv_tau, q_scale, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, R, part_len, max_parts, ws_state, ws_decay, stream);
 }
 
 extern "C" int gi_gated_group_norm(const float* y, const float* gate, int ld_gate, int gate_off, const float* weight, void* out, int out_dtype, int T, int W, int groups, float eps, int mode, float out_scale, void* stream) {

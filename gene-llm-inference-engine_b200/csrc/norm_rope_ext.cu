@@ -129,16 +129,35 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
                        const int* __restrict__ positions, const int* __restrict__ row_req,
                        const int* __restrict__ block_tables, int table_stride,
                        T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                       int H, int Hkv, int hd, int vd, int page_size, int write_kv) {
+                       int H, int Hkv, int hd, int vd, int page_size, int write_kv, int wide) {
     pdl_prologue();
     __shared__ float s_cos[kNrsMaxHead / 2], s_sin[kNrsMaxHead / 2];
+    __shared__ float s_wide[2][kNrsWarps];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = positions[t];
     const int half = freq ? rot_half : 0;
     for (int i = threadIdx.x; i < half; i += kNrsWarps * 32) sincosf(static_cast<float>(pos) * freq[i], &s_sin[i], &s_cos[i]);
-    __syncthreads();
     const float* row = in + static_cast<size_t>(t) * ld;
+    // wide: one unit-RMS norm over all query heads' values together (and one over all key heads'), the weights
+    // [H * hd] and [Hkv * hd]; every block of the token takes the two sums over the whole row in the same order
+    if (wide) {
+        float sq = 0.f, sk = 0.f;
+        if (q_norm) for (int i = threadIdx.x; i < H * hd; i += kNrsWarps * 32) sq = fmaf(row[q_off + i], row[q_off + i], sq);
+        if (k_norm) for (int i = threadIdx.x; i < Hkv * hd; i += kNrsWarps * 32) sk = fmaf(row[k_off + i], row[k_off + i], sk);
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { s_wide[0][warp] = sq; s_wide[1][warp] = sk; }
+    }
+    __syncthreads();
+    float wide_scale[2] = {1.f, 1.f};
+    if (wide) {
+        float sq = 0.f, sk = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNrsWarps; ++w) { sq += s_wide[0][w]; sk += s_wide[1][w]; }
+        wide_scale[0] = 1.0f / sqrtf(sq / static_cast<float>(H * hd) + eps);
+        wide_scale[1] = 1.0f / sqrtf(sk / static_cast<float>(Hkv * hd) + eps);
+    }
     size_t kv_base = 0, v_base = 0;       // in rows: a value row has vd values, a key row hd
     if (write_kv) {
         const int page = block_tables[static_cast<size_t>(row_req[t]) * table_stride + pos / page_size];
@@ -151,6 +170,7 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
         const bool is_q = head < H;
         const float* src = row + (is_q ? q_off + head * hd : k_off + (head - H) * hd);
         const float* nw = is_q ? q_norm : k_norm;
+        if (nw && wide) nw += (is_q ? head : head - H) * hd;
         float va[kNrsPairs], vb[kNrsPairs];
         int ia[kNrsPairs], ib[kNrsPairs];
         float ss = 0.f;
@@ -180,7 +200,7 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
         }
         if (nw) {
             ss = warp_sum(ss);
-            const float scale = 1.0f / sqrtf(ss / static_cast<float>(hd) + eps);
+            const float scale = wide ? wide_scale[is_q ? 0 : 1] : 1.0f / sqrtf(ss / static_cast<float>(hd) + eps);
 #pragma unroll
             for (int u = 0; u < kNrsPairs; ++u) {
                 if (lane + 32 * u < n_pairs) {
@@ -321,7 +341,7 @@ static int gi_norm_rope_store_impl(const float* in, int ld, int q_off, int k_off
                                    const float* k_norm, float eps, const float* freq, int rot_half, int interleaved,
                                    const int* positions, const int* row_req, const int* block_tables, int table_stride,
                                    void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd,
-                                   int vd, int page_size, int write_kv, void* stream) {
+                                   int vd, int page_size, int write_kv, int wide, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "norm_rope_store: sizes must be positive");
     GI_REQUIRE(hd <= kNrsMaxHead && hd % 2 == 0, "norm_rope_store: head size %d is odd or exceeds %d", hd, kNrsMaxHead);
@@ -337,12 +357,12 @@ static int gi_norm_rope_store_impl(const float* in, int ld, int q_off, int k_off
         launch_kernel((norm_rope_store_kernel<float>), dim3(T, head_blocks), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off, q_norm,
                       k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
                       static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
-                      vd, page_size, write_kv);
+                      vd, page_size, write_kv, wide);
     else if (dtype == kBF16)
         launch_kernel((norm_rope_store_kernel<__nv_bfloat16>), dim3(T, head_blocks), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off,
                       q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
                       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
-                      static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, vd, page_size, write_kv);
+                      static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, vd, page_size, write_kv, wide);
     else
         GI_REQUIRE(false, "norm_rope_store: unsupported dtype code %d", dtype);
     return check_launch("norm_rope_store");
@@ -360,8 +380,8 @@ extern "C" int gi_gated_act(const float* gate_up, const float* bias, void* out, 
     return gi::dispatch(gi_gated_act_impl, gate_up, bias, out, out_dtype, T, I, act, limit, stream);
 }
 
-extern "C" int gi_norm_rope_store(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_half, int interleaved, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int vd, int page_size, int write_kv, void* stream) {
-    return gi::dispatch(gi_norm_rope_store_impl, in, ld, q_off, k_off, v_off, q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride, q_out, k_cache, v_cache, dtype, T, H, Hkv, hd, vd, page_size, write_kv, stream);
+extern "C" int gi_norm_rope_store(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_half, int interleaved, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int vd, int page_size, int write_kv, int wide, void* stream) {
+    return gi::dispatch(gi_norm_rope_store_impl, in, ld, q_off, k_off, v_off, q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride, q_out, k_cache, v_cache, dtype, T, H, Hkv, hd, vd, page_size, write_kv, wide, stream);
 }
 
 static int gi_add_normed_impl(float* y, const float* weight, float* x, void* xn_out, int xn_dtype, int rows, int D, float eps,

@@ -58,6 +58,13 @@ softcap_kernel(float* __restrict__ z, float cap, float inv_cap, size_t total) {
         z[i] = cap * tanhf(z[i] * inv_cap);
 }
 
+__global__ void __launch_bounds__(256)
+scale_kernel(float* __restrict__ z, float factor, size_t total) {
+    pdl_prologue();
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * 256)
+        z[i] *= factor;
+}
+
 constexpr int kDepthKept = 4;          // pieces of a row that a thread keeps in registers between the two passes
 constexpr int kDepthWeights = 64;      // mixing weights held in shared memory (more are read from global memory)
 
@@ -242,6 +249,14 @@ static int gi_softcap_impl(float* z, long long total, float cap, void* stream) {
     return check_launch("softcap");
 }
 
+static int gi_scale_impl(float* z, long long total, float factor, void* stream) {
+    if (total == 0) return 0;
+    GI_REQUIRE(total > 0, "scale: the size must be positive");
+    launch_kernel(scale_kernel, dim3(grid_for(static_cast<size_t>(total))), dim3(256), 0, static_cast<cudaStream_t>(stream), z, factor,
+                  static_cast<size_t>(total));
+    return check_launch("scale");
+}
+
 static int gi_depth_mix_impl(float* x, float* y, const float* y_bias, float m, float* hist, int slots, int slot, const float* w, int first,
                              const float* next_weight, float eps, void* xn_out, int xn_dtype, int T, int D, void* stream) {
     if (T == 0) return 0;
@@ -280,6 +295,10 @@ extern "C" int gi_sigmoid_gate(const float* a, const float* g, long long ldg, in
 
 extern "C" int gi_softcap(float* z, long long total, float cap, void* stream) {
     return gi::dispatch(gi_softcap_impl, z, total, cap, stream);
+}
+
+extern "C" int gi_scale(float* z, long long total, float factor, void* stream) {
+    return gi::dispatch(gi_scale_impl, z, total, factor, stream);
 }
 
 extern "C" int gi_depth_mix(float* x, float* y, const float* y_bias, float m, float* hist, int slots, int slot, const float* w, int first,

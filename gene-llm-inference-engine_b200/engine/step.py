@@ -124,6 +124,11 @@ class StepContext:
         """A named range around some launches for profilers that show NVTX ranges (``StepEngine.nvtx``); free when off."""
         return _NvtxRange(name) if self._engine.nvtx else _NO_RANGE
 
+    @property
+    def tapping(self) -> bool:
+        """Whether someone listens to ``tap``: a block that keeps the stream in another form then also writes it out."""
+        return self._engine.tap is not None
+
     def tap(self, tag: str, layer: int, tensor: torch.Tensor) -> None:
         """Shows an intermediate activation to whoever listens (``StepEngine.tap``); the tags follow
         the reference's trace callback (src/model/model.h:16-22): "embedding", "attn_out" and

@@ -236,10 +236,11 @@ def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: 
                     k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], interleaved: bool,
                     positions: torch.Tensor, row_req: torch.Tensor, block_tables: torch.Tensor, q_out: torch.Tensor,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                    page_size: int, write_kv: bool = True, value_dim: Optional[int] = None) -> None:
+                    page_size: int, write_kv: bool = True, value_dim: Optional[int] = None, wide_norm: bool = False) -> None:
     """From the 32-bit projections ``proj`` [T, ld] (query heads from column q_offset, key heads from k_offset,
     value heads from v_offset, which may be the keys' columns): per head an optional unit-RMS norm with the
-    shared weight ``q_norm`` / ``k_norm`` [hd], then the rotation of the first 2 * len(freq) dimensions by
+    shared weight ``q_norm`` / ``k_norm`` [hd] (``wide_norm``: one norm over all query heads' values together and one
+    over all key heads', with weights [H*hd] and [Hkv*hd]), then the rotation of the first 2 * len(freq) dimensions by
     position * freq[i] (angles computed on the device in 32-bit), queries to ``q_out`` [T, H*hd], keys and
     values into the token's page row. ``value_dim``: the width of a value head when it is not the head size."""
     T, ld = proj.shape
@@ -250,9 +251,9 @@ def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: 
         raise KernelError("norm_rope_store: q_out and the cache must have one dtype")
     if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != (k_cache.shape[0], num_kv_heads, page_size, vd):
         raise KernelError("norm_rope_store: the cache must be [pages, Hkv, page_size, hd] (values: their own width)")
-    for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
-        if w is not None and w.numel() != head_dim:
-            raise KernelError(f"norm_rope_store: {name} must have head_dim values")
+    for w, name, heads in ((q_norm, "q_norm", num_heads), (k_norm, "k_norm", num_kv_heads)):
+        if w is not None and w.numel() != (heads * head_dim if wide_norm else head_dim):
+            raise KernelError(f"norm_rope_store: {name} must have head_dim values (all heads' with wide_norm)")
     check(lib().gi_norm_rope_store(
         _dev(proj, "proj", torch.float32), ld, int(q_offset), int(k_offset), int(v_offset),
         _opt(q_norm, "q_norm", torch.float32), _opt(k_norm, "k_norm", torch.float32), float(eps),
@@ -260,7 +261,7 @@ def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: 
         _dev(positions, "positions", torch.int32), _dev(row_req, "row_req", torch.int32),
         _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], _dev(q_out, "q_out"),
         _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), dtype_code(q_out.dtype), T, num_heads, num_kv_heads,
-        head_dim, vd, page_size, int(write_kv), _stream()), "norm_rope_store")
+        head_dim, vd, page_size, int(write_kv), int(bool(wide_norm)), _stream()), "norm_rope_store")
 
 
 def add_normed(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float, xn_out: Optional[torch.Tensor] = None,
@@ -306,6 +307,11 @@ def softcap(z: torch.Tensor, cap: float) -> None:
     check(lib().gi_softcap(_dev(z, "z", torch.float32), z.numel(), float(cap), _stream()), "softcap")
 
 
+def scale(z: torch.Tensor, factor: float) -> None:
+    """z <- factor * z in place, 32-bit."""
+    check(lib().gi_scale(_dev(z, "z", torch.float32), z.numel(), float(factor), _stream()), "scale")
+
+
 def depth_mix(x: torch.Tensor, y: torch.Tensor, mult: float, history: Optional[torch.Tensor] = None, slot: int = 0,
               weights: Optional[torch.Tensor] = None, first: bool = False, next_weight: Optional[torch.Tensor] = None,
               eps: float = 0.0, xn_out: Optional[torch.Tensor] = None, y_bias: Optional[torch.Tensor] = None) -> None:
@@ -327,6 +333,29 @@ def depth_mix(x: torch.Tensor, y: torch.Tensor, mult: float, history: Optional[t
                              slots, int(slot), _opt(weights, "weights", torch.float32), int(bool(first)),
                              _opt(next_weight, "next_weight", torch.float32), float(eps), 0 if xn_out is None else _dev(xn_out, "xn_out"),
                              F32 if xn_out is None else dtype_code(xn_out.dtype), T, D, _stream()), "depth_mix")
+
+
+def streams(X: torch.Tensor, single: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None, clear_y: bool = False,
+            mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None, in_w: Optional[torch.Tensor] = None,
+            norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, xn_out: Optional[torch.Tensor] = None,
+            sum_out: Optional[torch.Tensor] = None) -> None:
+    """Several copies of the residual stream, X [T, S, D] 32-bit. In one pass per row, any of: ``single`` [T, D]: the
+    copies are all this row (X is written from it); ``y`` [T, D] with ``mix`` [S, S] (indexed [from, to]) and ``out_w`` [S]:
+    every copy is rewritten at once, X'[t] = sum_s mix[s, t] X[s] + out_w[t] y (``clear_y``: y = 0 afterwards); ``in_w``
+    [S] with ``norm_weight`` [D] and ``eps``: xn_out = norm_weight * u / sqrt(mean(u^2) + eps) for u = sum_s in_w[s] X'[s];
+    ``sum_out`` [T, D] = sum_s X'[s]."""
+    T, S, D = X.shape
+    for t, name in ((single, "single"), (y, "y"), (xn_out, "xn_out"), (sum_out, "sum_out")):
+        if t is not None and t.shape != (T, D):
+            raise KernelError(f"streams: {name} must be [T, D]")
+    if (y is not None and (mix is None or out_w is None or mix.numel() != S * S or out_w.numel() != S)) or \
+            (in_w is not None and (in_w.numel() != S or norm_weight is None or norm_weight.numel() != D or xn_out is None)):
+        raise KernelError("streams: a rewrite needs mix [S, S] and out_w [S]; a read needs in_w [S], the norm's weight [D] and xn_out")
+    check(lib().gi_streams(_dev(X, "X", torch.float32), _opt(single, "single", torch.float32), _opt(y, "y", torch.float32),
+                           int(bool(clear_y)), _opt(mix, "mix", torch.float32), _opt(out_w, "out_w", torch.float32),
+                           _opt(in_w, "in_w", torch.float32), _opt(norm_weight, "norm_weight", torch.float32), float(eps),
+                           0 if xn_out is None else _dev(xn_out, "xn_out"), F32 if xn_out is None else dtype_code(xn_out.dtype),
+                           _opt(sum_out, "sum_out", torch.float32), T, S, D, _stream()), "streams")
 
 
 def latent_store(proj: torch.Tensor, q_offset: int, q_weight: Optional[torch.Tensor], q_latent: Optional[torch.Tensor],
@@ -398,11 +427,13 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[tor
                    num_kv_heads: int, head_dim: int, value_dim: int, page_size: int, scale: float,
                    window: Optional[int] = None, chunk: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
                    sinks: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
-                   tiles: Optional[torch.Tensor] = None, splits: int = 1, workspace: Optional[torch.Tensor] = None) -> None:
+                   tiles: Optional[torch.Tensor] = None, splits: int = 1, workspace: Optional[torch.Tensor] = None,
+                   softcap: Optional[float] = None) -> None:
     """Attention of every row of ``q`` [T, H*hd] (32-bit or bfloat16) over its request's pages, 32-bit arithmetic.
     ``v_cache`` None: the values are the first ``value_dim`` columns of the key rows. ``window``: the last w positions;
     ``chunk``: only keys of the query's own block of c positions; ``slopes`` [H]: slope_h * distance is taken off a
-    score; ``sinks`` [H]: exp(sinks_h) more in the softmax's denominator. ``out`` [T, H*vd], 32-bit or bfloat16.
+    score; ``sinks`` [H]: exp(sinks_h) more in the softmax's denominator; ``softcap`` c: the scaled score s becomes
+    c tanh(s / c). ``out`` [T, H*vd], 32-bit or bfloat16.
     (See attention_rows_tensor_cores for the form that rounds queries and softmax weights to bfloat16.)
     Tensor-core form only (attention_rows_tile_tokens() > 0): ``rows`` [n] lists the step rows to work on, a tile each;
     ``tiles`` [m, 3] = (first row, tokens (at most attention_rows_tile_tokens()), request) lists tiles of consecutive
@@ -428,7 +459,7 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[tor
         dtype_code(k_cache.dtype), _dev(out, "out"), dtype_code(out.dtype), out.shape[1], _dev(row_req, "row_req", torch.int32),
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], T,
         num_heads, num_kv_heads, head_dim, value_dim, head_dim if v_cache is None else value_dim, int(v_cache is None), page_size,
-        float(scale), int(window or 0), int(chunk or 0), _opt(slopes, "slopes", torch.float32), _opt(sinks, "sinks", torch.float32),
+        float(scale), float(softcap or 0.0), int(window or 0), int(chunk or 0), _opt(slopes, "slopes", torch.float32), _opt(sinks, "sinks", torch.float32),
         _opt(lst, "rows or tiles", torch.int32), kind, n_list, int(splits), _opt(workspace, "workspace", torch.float32),
         0 if workspace is None else workspace.numel(), _stream()), "attention_rows")
     if splits > 1:
@@ -438,11 +469,11 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[tor
 def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
                            tables: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
                            window: Optional[int], chunk: Optional[int], slopes: Optional[torch.Tensor],
-                           sinks: Optional[torch.Tensor]) -> None:
+                           sinks: Optional[torch.Tensor], softcap: Optional[float] = None) -> None:
     """``attention_rows`` for all rows of a step. Over a bfloat16 cache with sizes that the tensor-core form serves, the
     step's single tokens and the tiles of its prompt portions (``ctx.attention_work``) run as two launches, each with its
     keys cut into ranges when it has few tiles; otherwise one launch works row by row."""
-    common = dict(window=window, chunk=chunk, slopes=slopes, sinks=sinks)
+    common = dict(window=window, chunk=chunk, slopes=slopes, sinks=sinks, softcap=softcap)
     per_tile = attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, v_cache is None) \
         if k_cache.dtype is torch.bfloat16 else 0
     if per_tile == 0 or not hasattr(ctx, "attention_work"):
@@ -618,25 +649,26 @@ def route_combine(part: torch.Tensor, weights: torch.Tensor, y: torch.Tensor, pa
                                  _opt(pair_row, "pair_row", torch.int32), _dev(y, "y", torch.float32), T, D, top, _stream()), "route_combine")
 
 
-def causal_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+def causal_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                 state_offset: int, row_req: torch.Tensor, seg_start: torch.Tensor, seg_len: torch.Tensor,
-                state_slots: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, c] = silu(bias[c] + sum_j weight[c, j] * u(t - taps + 1 + j, c)) over the channels
+                state_slots: torch.Tensor, out: torch.Tensor, activate: bool = True) -> None:
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] * u(t - taps + 1 + j, c)) (act: SiLU, or nothing when ``activate``
+    is off; ``bias`` may be None) over the channels
     proj[:, offset:offset + C] of each request's rows; inputs before a segment's first row come from the request's
     state (``state`` [slots, floats per slot], the [taps-1, C] block at ``state_offset``), which afterwards
     holds the last taps-1 inputs. Two launches."""
     T, ld = proj.shape
     C, taps = weight.shape
-    if out.shape != (T, C) or bias.numel() != C:
+    if out.shape != (T, C) or (bias is not None and bias.numel() != C):
         raise KernelError("causal_conv: shapes of weight, bias and out do not agree")
     if state.dim() != 2 or state_offset < 0 or state_offset + (taps - 1) * C > state.shape[1]:
         raise KernelError("causal_conv: the conv state does not fit the slot")
     R = seg_start.numel()
     check(lib().gi_causal_conv(_dev(proj, "proj", torch.float32), ld, int(offset), _dev(weight, "weight", torch.float32),
-                               _dev(bias, "bias", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
+                               _opt(bias, "bias", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
                                int(state_offset), _dev(row_req, "row_req", torch.int32), _dev(seg_start, "seg_start", torch.int32),
                                _dev(seg_len, "seg_len", torch.int32), _dev(state_slots, "state_slots", torch.int32),
-                               _dev(out, "out", torch.float32), C, taps, T, R, _stream()), "causal_conv")
+                               _dev(out, "out", torch.float32), C, taps, T, R, int(bool(activate)), _stream()), "causal_conv")
     if taps > 1:
         count_launches(1)
 
@@ -647,16 +679,19 @@ def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, 
                 decay: Optional[torch.Tensor] = None, dt: Optional[torch.Tensor] = None, dt_offset: int = 0,
                 dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
                 skip: Optional[torch.Tensor] = None, part_len: int = 0, ws_state: Optional[torch.Tensor] = None,
-                ws_decay: Optional[torch.Tensor] = None) -> None:
+                ws_decay: Optional[torch.Tensor] = None, row_gate: Optional[torch.Tensor] = None, row_gate_offset: int = 0,
+                row_gate_bias: Optional[torch.Tensor] = None, tau: float = 1.0, q_scale: float = 1.0) -> None:
     """The recurrence S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t + skip * v_t per head over each
     request's rows in order, the state [H, dk, dv] carried in the request's slot of ``state`` [slots, floats]
     at ``state_offset``. q, k [T, ld] hold H / group heads of dk from their offsets (head h reads head
     h // group), v holds H heads of dv. Either ``decay`` [H] (a constant, b = 1) or ``dt`` [T, ld] with
-    ``dt_bias`` and ``a_log`` [H] (dt' = softplus(dt + bias), a = exp(-exp(a_log) dt'), b = dt').
-    ``activate``: SiLU on q, k, v as they are read. All 32-bit.
+    ``dt_bias`` and ``a_log`` [H] (dt' = softplus(dt + bias), a = exp(-exp(a_log) dt'), b = dt'), or ``row_gate``
+    [T, ld] holding z for every head and key channel from ``row_gate_offset`` (plus ``row_gate_bias`` [H*dk]): row i of
+    head h's state then fades by its own factor sigmoid(z)^(1/``tau``) per token, b = 1 (group must be 1).
+    ``q_scale``: a constant on the queries. ``activate``: SiLU on q, k, v as they are read. All 32-bit.
     ``part_len`` > 0 cuts segments into parts of that many tokens which run side by side (three launches: the
     parts from zero states, the parts' start states, what the start states add); it needs ``ws_state``
-    [scan_parts(T, R, part_len), H * dk * dv] and ``ws_decay`` [T, H]. Results differ from the one-launch form by
+    [scan_parts(T, R, part_len), H * dk * dv] and ``ws_decay`` [T, H] ([T, H * dk] with ``row_gate``). Results differ from the one-launch form by
     rounding only."""
     T = out.shape[0]
     if out.shape != (T, num_heads * dv):
@@ -665,7 +700,12 @@ def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, 
     for t, off, width, name in ((q, q_offset, kv_heads * dk, "q"), (k, k_offset, kv_heads * dk, "k"), (v, v_offset, num_heads * dv, "v")):
         if t.dim() != 2 or t.shape[0] != T or off < 0 or off + width > t.shape[1]:
             raise KernelError(f"linear_scan: {name} does not hold its heads inside a row")
-    if decay is None and (dt is None or dt_bias is None or a_log is None or dt_offset + num_heads > dt.shape[1]):
+    if row_gate is not None:
+        if decay is not None or dt is not None or group != 1 or row_gate.dim() != 2 or row_gate.shape[0] != T or \
+                row_gate_offset < 0 or row_gate_offset + num_heads * dk > row_gate.shape[1] or not tau > 0 or \
+                (row_gate_bias is not None and row_gate_bias.numel() != num_heads * dk):
+            raise KernelError("linear_scan: per-row decays come alone, one key head per head, their columns inside a row")
+    elif decay is None and (dt is None or dt_bias is None or a_log is None or dt_offset + num_heads > dt.shape[1]):
         raise KernelError("linear_scan: give constant decays or step sizes with their bias and rates")
     for t, name in ((decay, "decay"), (dt_bias, "dt_bias"), (a_log, "a_log"), (skip, "skip")):
         if t is not None and t.numel() != num_heads:
@@ -677,13 +717,15 @@ def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, 
     if part_len:
         max_parts = (T + part_len - 1) // part_len          # no segment is longer than the step
         if ws_state is None or ws_decay is None or ws_state.numel() < scan_parts(T, R, part_len) * num_heads * dk * dv or \
-                ws_decay.numel() < T * num_heads:
+                ws_decay.numel() < T * num_heads * (dk if row_gate is not None else 1):
             raise KernelError("linear_scan: the workspaces of the parts are missing or too small")
     check(lib().gi_linear_scan(
         _dev(q, "q", torch.float32), q.shape[1], int(q_offset), _dev(k, "k", torch.float32), k.shape[1], int(k_offset),
         _dev(v, "v", torch.float32), v.shape[1], int(v_offset), num_heads, group, dk, dv, int(bool(activate)),
         _opt(decay, "decay", torch.float32), _opt(dt, "dt", torch.float32), 0 if dt is None else dt.shape[1], int(dt_offset),
         _opt(dt_bias, "dt_bias", torch.float32), _opt(a_log, "a_log", torch.float32), _opt(skip, "skip", torch.float32),
+        _opt(row_gate, "row_gate", torch.float32), 0 if row_gate is None else row_gate.shape[1], int(row_gate_offset),
+        _opt(row_gate_bias, "row_gate_bias", torch.float32), 1.0 / float(tau), float(q_scale),
         _dev(state, "state", torch.float32), state.shape[1], int(state_offset), _dev(seg_start, "seg_start", torch.int32),
         _dev(seg_len, "seg_len", torch.int32), _dev(state_slots, "state_slots", torch.int32), _dev(out, "out", torch.float32),
         R, int(part_len), max_parts, _opt(ws_state, "ws_state", torch.float32), _opt(ws_decay, "ws_decay", torch.float32),
@@ -701,16 +743,17 @@ def scan_parts(T: int, R: int, part_len: int = SCAN_PART) -> int:
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor,
-                     groups: int, eps: float, gate_first: bool, out_scale: float = 1.0) -> None:
+                     groups: int, eps: float, gate_first: bool, out_scale: float = 1.0, gate_act: str = "sigmoid") -> None:
     """Unit-RMS norm of y [T, W] in ``groups`` equal parts, times ``weight`` [W], with a gate from
     gate[:, gate_offset:gate_offset + W]: ``gate_first`` norms y * silu(gate); else the normed values are multiplied
-    by sigmoid(gate). ``out_scale``: a constant factor."""
+    by sigmoid(gate) or, with ``gate_act`` "silu", by silu(gate). ``out_scale``: a constant factor."""
     T, W = y.shape
     if out.shape != (T, W) or weight.numel() != W or gate.dim() != 2 or gate.shape[0] != T:
         raise KernelError("gated_group_norm: shapes do not agree")
     check(lib().gi_gated_group_norm(_dev(y, "y", torch.float32), _dev(gate, "gate", torch.float32), gate.shape[1],
                                     int(gate_offset), _dev(weight, "weight", torch.float32), _dev(out, "out"),
-                                    dtype_code(out.dtype), T, W, int(groups), float(eps), int(bool(gate_first)),
+                                    dtype_code(out.dtype), T, W, int(groups), float(eps),
+                                    1 if gate_first else 2 if gate_act == "silu" else 0,
                                     float(out_scale), _stream()), "gated_group_norm")
 
 

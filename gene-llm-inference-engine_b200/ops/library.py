@@ -33,12 +33,12 @@ _SIGNATURES = {
     "gi_gated_act": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "gi_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                           c_int, c_int, c_int, c_int, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_void_p],
     "gi_add_normed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "gi_latent_store": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                         c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "gi_attention_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "gi_attention_rows_tile_tokens": [c_int, c_int, c_int, c_int, c_int],
     "gi_attention_rows_supported": [c_int, c_int],
@@ -59,13 +59,17 @@ _SIGNATURES = {
     "gi_add_bias": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "gi_sigmoid_gate": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "gi_softcap": [c_void_p, c_longlong, c_float, c_void_p],
+    "gi_scale": [c_void_p, c_longlong, c_float, c_void_p],
     "gi_depth_mix": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
                      c_int, c_int, c_void_p],
+    "gi_streams": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
+                   c_int, c_int, c_int, c_void_p],
     "gi_grouped_tile_rows": [],
     "gi_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "gi_linear_scan": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                       c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                       c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_int, c_int, c_void_p, c_float, c_float, c_void_p, c_longlong,
                        c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "gi_gated_group_norm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_float, c_void_p],

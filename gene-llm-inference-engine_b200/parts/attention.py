@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..cache import CacheNeed
+from ..cache import CacheNeed, StateNeed
 from ..config import PartSpec
 from ..ops import kernels
 from ..ops.linear import Linear
@@ -35,7 +35,14 @@ class AttentionMixer:
     queries and keys has no weights. ``distance_slopes`` [H]: slope_h * (i - j) is taken off the score of key j for the
     query at i. ``chunk``: position i sees j <= i only inside its own block of ``chunk`` positions counted from 0
     (pages of earlier blocks are given back). ``sink`` = "learned": the term added to the softmax's denominator is
-    exp(``sink``_h) with a weight per head (``sink`` [H])."""
+    exp(``sink``_h) with a weight per head (``sink`` [H]). ``softcap`` c: the scaled score s becomes c tanh(s / c).
+
+    ``qk_norm_wide`` (with ``qk_norm_eps``): the norm runs over the whole query projection at once (all heads' values
+    together, ``q_norm`` [H * hd]) and over the whole key projection (``k_norm`` [Hkv * hd]) instead of head by head.
+    ``conv_taps`` n > 1: every channel of the [q; k; v] projection passes a causal convolution over the request's last n
+    tokens before anything else (``conv`` [channels, n], column n-1 weighs the newest token; no bias, no activation;
+    nothing before the first token); the request's last n-1 projected rows are state, kept in its state slot from
+    ``state_offset`` on."""
 
     graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
 
@@ -61,22 +68,29 @@ class AttentionMixer:
         self.value_dim = int(params.get("value_dim") or self.head_dim)
         self.chunk = params.get("chunk")
         self.learned_sink = params.get("sink") == "learned"
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError("attention: the soft cap of the scores must be positive")
+        self.wide_norm = bool(params.get("qk_norm_wide", False))
+        self.conv_taps = int(params.get("conv_taps") or 1)
+        self.state_offset = 0
         slopes = params.get("distance_slopes")
         if slopes is not None and len(slopes) != self.num_heads:
             raise ValueError("attention: distance_slopes needs one slope per head")
         self.slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32, device=build.device)
         # these options are served by the row-form kernel only
-        self.row_form = (self.value_dim != self.head_dim or self.chunk is not None or self.learned_sink or self.slopes is not None)
+        self.row_form = (self.value_dim != self.head_dim or self.chunk is not None or self.learned_sink or
+                         self.slopes is not None or self.softcap is not None)
         self.sink = bool(params.get("sink", False))
         self.head_gate = bool(params.get("head_gate", False))
         self.out_scale = float(params.get("out_scale", 1.0))
         on_device = getattr(self.position, "freq", None) is not None
         self.extended = (self.values_are_keys or self.qk_norm_eps is not None or self.sink or self.head_gate
-                         or self.out_scale != 1.0 or on_device or self.row_form)
+                         or self.out_scale != 1.0 or on_device or self.row_form or self.conv_taps > 1)
         if self.row_form:
             if self.head_gate or self.out_scale != 1.0 or self.values_are_keys:
                 raise ValueError("attention: a gate, an output factor or values taken from the keys cannot be combined with "
-                                 "value_dim, chunk, distance_slopes or a learned sink")
+                                 "value_dim, chunk, distance_slopes, a soft cap or a learned sink")
             if not kernels.attention_rows_supported(self.head_dim, self.value_dim):
                 raise ValueError(f"attention: head size {self.head_dim} with value size {self.value_dim} is not supported")
         if getattr(self.position, "amplitude", 1.0) != 1.0:
@@ -95,10 +109,13 @@ class AttentionMixer:
         if self.qk_norm_eps is not None and not params.get("qk_norm_weights", True):
             self.q_norm = self.k_norm = torch.ones(self.head_dim, dtype=torch.float32, device=build.device)
         elif self.qk_norm_eps is not None:
-            for name in ("q_norm", "k_norm"):
-                if tuple(weights[name].shape) != (self.head_dim,):
-                    raise ValueError(f"attention: {name} has shape {tuple(weights[name].shape)}, expected ({self.head_dim},)")
+            for name, heads in (("q_norm", self.num_heads), ("k_norm", self.num_kv_heads)):
+                n = heads * self.head_dim if self.wide_norm else self.head_dim
+                if tuple(weights[name].shape) != (n,):
+                    raise ValueError(f"attention: {name} has shape {tuple(weights[name].shape)}, expected ({n},)")
                 setattr(self, name, weights[name].to(device=build.device, dtype=torch.float32).contiguous())
+        if self.wide_norm and (self.qk_norm_eps is None or not params.get("qk_norm_weights", True)):
+            raise ValueError("attention: qk_norm_wide needs qk_norm_eps and weights")
         qkv_rows = (self.num_heads + self.num_kv_heads) * self.head_dim + \
             (0 if self.values_are_keys else self.num_kv_heads * self.value_dim) + (self.num_heads if self.head_gate else 0)
         if tuple(weights["w_qkv"].shape) != (qkv_rows, self.hidden_size):
@@ -106,6 +123,16 @@ class AttentionMixer:
                              f"({qkv_rows}, {self.hidden_size})")
         if tuple(weights["w_o"].shape) != (self.hidden_size, self.num_heads * self.value_dim):
             raise ValueError(f"attention: w_o has shape {tuple(weights['w_o'].shape)}")
+        self.conv = None
+        if self.conv_taps > 1:
+            if self.head_gate or self.values_are_keys:
+                raise ValueError("attention: a convolution of the projections cannot be combined with a head gate or values taken from the keys")
+            if not (self.conv_taps <= 17):
+                raise ValueError(f"attention: {self.conv_taps} convolution taps are not supported (1 to 17)")
+            if tuple(weights["conv"].shape) != (qkv_rows, self.conv_taps):
+                raise ValueError(f"attention: conv has shape {tuple(weights['conv'].shape)}, expected ({qkv_rows}, {self.conv_taps})")
+            self.conv = weights["conv"].to(device=build.device, dtype=torch.float32).contiguous()
+            self.conv_channels = qkv_rows
         self.w_qkv = Linear(weights["w_qkv"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
@@ -137,9 +164,15 @@ class AttentionMixer:
                          value_dim=None if self.value_dim == self.head_dim else self.value_dim, chunk=self.chunk)
 
     def state_need(self):
-        return None
+        if self.conv is None:
+            return None
+        return StateNeed(((self.conv_taps - 1) * self.conv_channels,), "float32")
 
     def launch_key(self, ctx, run):
+        key = self._launch_key(ctx, run)
+        return key + (ctx.n_requests,) if self.conv is not None else key
+
+    def _launch_key(self, ctx, run):
         """What the mixer's launches depend on besides the token count: whose cache it uses, and (tensor-core
         kernels) how many rows are single decoded tokens, how many tiles the prompt portions make and how many
         chunks the longest context of a single token has. Asking also places this step's work lists on the device."""
@@ -217,17 +250,22 @@ class AttentionMixer:
         H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         proj = ctx.scratch("att_proj", (T, self.w_qkv.out_features), torch.float32)
         self.w_qkv.forward(xn, proj)
+        if self.conv is not None:
+            mixed = ctx.scratch("att_proj_conv", (T, self.conv_channels), torch.float32)
+            kernels.causal_conv(proj, 0, self.conv, None, ctx.state(run.cache_layer), self.state_offset, ctx.row_req,
+                                ctx.seg_start, ctx.seg_len, ctx.state_slots, mixed, activate=False)
+            proj = mixed
         k_off = H * hd
         v_off = k_off if self.values_are_keys else k_off + Hkv * hd
         gate_off = v_off + Hkv * hd
         kernels.norm_rope_store(proj, 0, k_off, v_off, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
                                 getattr(self.position, "freq", None), self.position.interleaved, ctx.positions,
                                 ctx.row_req, tables, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
-                                write_kv=run.writes_cache, value_dim=self.value_dim)
+                                write_kv=run.writes_cache, value_dim=self.value_dim, wide_norm=self.wide_norm)
         if self.row_form:
             att = ctx.scratch("att", (T, H * self.value_dim), self.dtype)
             kernels.attention_rows_of_step(ctx, q, k_cache, v_cache, att, tables, H, Hkv, hd, self.value_dim, self.scale,
-                                           self.window, self.chunk, self.slopes, self.sink_weight)
+                                           self.window, self.chunk, self.slopes, self.sink_weight, softcap=self.softcap)
             self.w_o.forward(att, x, accumulate=True, then=then)
             return
         att = ctx.scratch("att", (T, H * hd), self.dtype)

@@ -248,6 +248,108 @@ class ParallelBlock:
             carry["parallel"] = (x.data_ptr(), nxt, bool(self.slot))
 
 
+@register_block("hyper_connections")
+class HyperConnectionBlock:
+    """A pre-norm layer over several copies X[0..S-1] of the residual stream instead of one. Sublayer q (1: the mixer, 2: the
+    feed-forward, which a layer may lack) reads u = sum_s a_q[s] X[s], computes y = sublayer(N_q(u)), and every copy is then
+    rewritten at once from the old ones: X'[t] = sum_s M_q[s, t] X[s] + b_q[t] y. The first block of this kind in a row
+    starts from copies that all equal the stream it is handed; the last one leaves the sum of the copies there.
+    ``block_params``: ``streams`` (S). Weights: ``hc1.in`` [S], ``hc1.out`` [S], ``hc1.mix`` [S, S] (indexed [from, to]) and the
+    same under ``hc2.``.
+
+    The copies are 32-bit, [tokens, S, width], scratch of the step. A sublayer adds into ``y``, which is zero when it starts.
+    One kernel per sublayer rewrites the copies, clears y and writes the normed input of the sublayer that runs next (the
+    feed-forward's, or the next block's mixer's when that block is of this kind with as many copies) in the same pass, so a
+    layer costs one memory-bound kernel per sublayer beside the sublayers (``ctx.carry`` tells the next block what it finds)."""
+
+    def __init__(self, layer_spec, weights, build):
+        self.streams = int(layer_spec.block_params["streams"])
+        if not (1 <= self.streams <= 8):
+            raise ValueError(f"hyper-connection block: {self.streams} copies of the stream are not supported (1 to 8)")
+        self.mixer_norm = build_part(NORMS, "norm", layer_spec.mixer_norm, sub_weights(weights, "mixer_norm."), build)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, sub_weights(weights, "mixer."), build)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward_norm = build_part(NORMS, "norm", layer_spec.feed_forward_norm,
+                                                sub_weights(weights, "feed_forward_norm."), build)
+            self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward,
+                                           sub_weights(weights, "feed_forward."), build)
+        S = self.streams
+        self.connections = []
+        for q in (1, 2) if self.feed_forward is not None else (1,):
+            got = {}
+            for name, shape in (("in", (S,)), ("out", (S,)), ("mix", (S, S))):
+                w = weights[f"hc{q}.{name}"]
+                if tuple(w.shape) != shape:
+                    raise ValueError(f"hyper-connection block: hc{q}.{name} has shape {tuple(w.shape)}, expected {shape}")
+                got[name] = w.to(device=build.device, dtype=torch.float32).contiguous()
+            self.connections.append(got)
+        self.dtype = build.compute_dtype
+        self._next = {}             # run (by the layer whose cache it uses) -> the block that runs after it, when of this kind
+
+    def followed_in_run(self, run, block) -> None:
+        ok = isinstance(block, HyperConnectionBlock) and block.streams == self.streams
+        self._next[run.cache_layer] = block if ok else None
+
+    def forward(self, ctx, run, x: torch.Tensor) -> None:
+        from ..ops import kernels
+        T, D = x.shape
+        S = self.streams
+        X = ctx.scratch("stream_copies", (T, S, D), torch.float32)
+        y = ctx.scratch("stream_y", (T, D), torch.float32)
+        xn = ctx.scratch("normed", (T, D), self.dtype)
+        carry = getattr(ctx, "carry", None)
+        state = carry.get("stream_copies") if carry is not None else None
+        # what the block before left: the copies, y = 0 and xn = this block's normed input
+        ready = state is not None and state == (x.data_ptr(), id(self))
+        nxt = self._next.get(run.cache_layer)
+        show = bool(getattr(ctx, "tapping", False))
+        first, second = self.connections[0], (self.connections[1] if self.feed_forward is not None else None)
+
+        def rewrite(con, to_norm, to_in, sum_out):
+            kernels.streams(X, y=y, clear_y=True, mix=con["mix"], out_w=con["out"], in_w=to_in,
+                            norm_weight=None if to_norm is None else to_norm.weight,
+                            eps=0.0 if to_norm is None else to_norm.eps, xn_out=None if to_norm is None else xn, sum_out=sum_out)
+
+        def after(sum_now):
+            """What the kernel that ends this block's last sublayer prepares: the next block's read, or the sum of the copies."""
+            if nxt is not None:
+                return nxt.mixer_norm, nxt.connections[0]["in"], (x if sum_now else None)
+            return None, None, x
+
+        def mixer_half():
+            if not ready:
+                kernels.scale_cast(x, y, None, 0.0)                                   # y = 0
+                kernels.streams(X, single=x, in_w=first["in"], norm_weight=self.mixer_norm.weight, eps=self.mixer_norm.eps, xn_out=xn)
+            self.mixer.forward(ctx, run, xn, y)
+            if second is not None:
+                rewrite(first, self.feed_forward_norm, second["in"], x if show else None)
+            else:
+                rewrite(first, *after(show))
+
+        key = _launch_key(ctx, (self.mixer_norm, None), (self.mixer, run))
+        if key is not None:
+            ctx.recorded(self, ("mixer", run, T, ready) + key, mixer_half)
+        else:
+            mixer_half()
+        ctx.tap("attn_out", run.layer, x)
+        if second is not None:
+            def feed_forward_half():
+                self.feed_forward.forward(ctx, xn, y)
+                rewrite(second, *after(show))
+            key = _launch_key(ctx, (self.feed_forward_norm, None), (self.feed_forward, None))
+            if key is not None:
+                ctx.recorded(self, ("feed_forward", run, T) + key, feed_forward_half)
+            else:
+                feed_forward_half()
+        ctx.tap("ffn_out", run.layer, x)
+        if carry is not None:
+            if nxt is not None:
+                carry["stream_copies"] = (x.data_ptr(), id(nxt))
+            else:
+                carry.pop("stream_copies", None)
+
+
 def build_extra(layer_spec, key: str, table, what: str, weights, build):
     """Builds the part that a layer's ``extra`` names ``key`` (for arrangements with more parts than
     the usual four), with the weights under ``<key>.``."""

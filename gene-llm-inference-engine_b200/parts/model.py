@@ -71,6 +71,9 @@ class DecoderModel:
             follows = getattr(self.layers[run.layer], "followed_by", None)
             if follows is not None:
                 follows(self.layers[after.layer])
+            follows = getattr(self.layers[run.layer], "followed_in_run", None)      # for a layer that runs more than once
+            if follows is not None:
+                follows(run, self.layers[after.layer])
         if spec.tie_word_embeddings:
             self.head = Linear.over(self.embedding, tiles=weight_tiles)   # the table itself, not a second row-major copy
         else:

@@ -9,12 +9,12 @@ import torch
 from .registry import register_logit_transform, register_position_encoding
 
 
-def rope_frequencies(head_dim: int, theta: float, scaling, rotary_dim=None) -> np.ndarray:
+def rope_frequencies(head_dim: int, theta: float, scaling, rotary_dim=None, round_theta: bool = True) -> np.ndarray:
     """Rotation frequency of each pair in double precision: 1/theta^(2k/rotary_dim), with the
     "llama3" scaling when given (src/kernels/kernels.cpp:142-163). theta is rounded to 32-bit
     first, as the reference stores it so (src/loader/hf_checkpoint.cpp:125)."""
     rd = rotary_dim or head_dim
-    theta = float(np.float32(theta))
+    theta = float(np.float32(theta)) if round_theta else float(theta)
     k = np.arange(rd // 2, dtype=np.float64)
     freq = 1.0 / np.power(theta, 2.0 * k / rd)
     if scaling:
@@ -85,7 +85,12 @@ class RotaryOnDevice:
     ``original`` positions: with n(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) the index of the pair that
     turns t times within ``original`` positions, lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), rotary_dim - 1)
     and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i (1 - r_i) + f_i r_i / factor, and
-    cos and sin are multiplied by ``amplitude`` = 0.1 ln(factor) + 1 (1 without scaling)."""
+    cos and sin are multiplied by ``amplitude`` = 0.1 ln(factor) + 1 (1 without scaling).
+
+    Optional ``wavelength_scaling`` {factor, low, high, original}: a pair whose wavelength 2 pi / f is shorter than
+    original / high keeps f, one whose wavelength is longer than original / low turns at f / factor, and between the two
+    f (1 - s) / factor + f s with s = (original / wavelength - low) / (high - low) (the frequencies of ``rope_frequencies``
+    with its "llama3" scaling, computed once in double)."""
 
     applies = "qk_before_store"
     cos = None
@@ -118,6 +123,13 @@ class RotaryOnDevice:
             r = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
             freq = freq / factor * r + freq * (1.0 - r)
             self.amplitude = 0.1 * math.log(factor) + 1.0
+        wave = params.get("wavelength_scaling")
+        if wave:
+            if ramp:
+                raise ValueError("rope: ramp_scaling and wavelength_scaling exclude one another")
+            freq = rope_frequencies(self.head_dim, float(params["theta"]), {
+                "factor": wave["factor"], "low_freq_factor": wave["low"], "high_freq_factor": wave["high"],
+                "original_max_position": wave["original"]}, self.rotary_dim, round_theta=False)
         self.freq = torch.from_numpy(freq.astype(np.float32)).to(build.device).contiguous()
 
 
@@ -157,3 +169,15 @@ class SoftCap:
     def forward(self, ctx, logits: torch.Tensor) -> None:
         from ..ops import kernels
         kernels.softcap(logits, self.cap)
+
+
+@register_logit_transform("scale")
+class LogitScale:
+    """logits <- factor * logits, in place, 32-bit. Params: ``factor``."""
+
+    def __init__(self, params, weights, build):
+        self.factor = float(params["factor"])
+
+    def forward(self, ctx, logits: torch.Tensor) -> None:
+        from ..ops import kernels
+        kernels.scale(logits, self.factor)

@@ -1,9 +1,11 @@
 """Mixers that keep a state of fixed size per request instead of keys and values.
 
-Both run the same recurrence kernel, M_t = a_t M_(t-1) + b_t k_t (x) v_t and y_t = M_t^T q_t (+ skip v_t), per
+All run the same recurrence kernel, M_t = a_t M_(t-1) + b_t k_t (x) v_t and y_t = M_t^T q_t (+ skip v_t), per
 head over each request's rows in order, with the 32-bit state [H, dk, dv] in the request's state slot
 (``ctx.state(layer)[slot]``; the engine hands a new request a zeroed slot). They differ in where q, k, v, a and
-b come from and in the gated norm that follows.
+b come from (a may be a number per head, per head and token, or per row of M and token) and in the gated norm
+that follows. A mixer's state begins at ``state_offset`` floats into the slot (0 unless a mixer that holds several
+state-keeping mixers moves it).
 """
 from __future__ import annotations
 
@@ -15,16 +17,17 @@ from ..ops.linear import Linear
 from .registry import register_mixer
 
 
-def _scan_workspaces(ctx, T: int, H: int, dk: int, dv: int):
+def _scan_workspaces(ctx, T: int, H: int, dk: int, dv: int, row_decays: bool = False):
     """(part_len, ws_state, ws_decay) for a step's recurrence: segments that fit one part run in one launch on the
-    state slot itself; longer ones are cut into parts that run side by side (kernels.linear_scan)."""
+    state slot itself; longer ones are cut into parts that run side by side (kernels.linear_scan). ``row_decays``:
+    the running products of the decays are kept per row of the state."""
     if T <= kernels.SCAN_PART:
         return {}
     R = ctx.n_requests
     parts = kernels.scan_parts(T, R)
     most = getattr(ctx, "max_step_tokens", T) // kernels.SCAN_PART + ctx.max_requests
     ws_state = ctx.scratch("scan_part_states", (parts, H * dk * dv), torch.float32, capacity=max(parts, most))
-    ws_decay = ctx.scratch("scan_decays", (T, H), torch.float32)
+    ws_decay = ctx.scratch("scan_row_decays" if row_decays else "scan_decays", (T, H * dk if row_decays else H), torch.float32)
     return {"part_len": kernels.SCAN_PART, "ws_state": ws_state, "ws_decay": ws_decay}
 
 
@@ -73,6 +76,7 @@ class LinearAttentionMixer:
         self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.norm = _vector(weights, "norm", H * dv, build, "linear attention")
         self.dtype = build.compute_dtype
+        self.state_offset = 0
 
     def cache_need(self):
         return None
@@ -92,7 +96,7 @@ class LinearAttentionMixer:
         self.w_in.forward(xn, proj)
         o = ctx.scratch("lin_att_out", (T, H * dv), torch.float32)
         kernels.linear_scan(proj, 0, proj, H * dk, proj, 2 * H * dk, H, 1, dk, dv, self.activate,
-                            ctx.state(run.cache_layer), 0, ctx.seg_start, ctx.seg_len, ctx.state_slots, o, decay=self.decay,
+                            ctx.state(run.cache_layer), self.state_offset, ctx.seg_start, ctx.seg_len, ctx.state_slots, o, decay=self.decay,
                             **_scan_workspaces(ctx, T, H, dk, dv))
         y = ctx.scratch("lin_att_normed", (T, H * dv), self.dtype)
         kernels.gated_group_norm(o, proj, 2 * H * dk + H * dv, self.norm, y, 1, self.eps, gate_first=False,
@@ -152,6 +156,7 @@ class StateSpaceMixer:
         self.skip = _vector(weights, "skip", H, build, "state space")
         self.norm = _vector(weights, "norm", self.inner, build, "state space")
         self.dtype = build.compute_dtype
+        self.state_offset = 0
 
     def cache_need(self):
         return None
@@ -172,11 +177,11 @@ class StateSpaceMixer:
         proj = ctx.scratch("ssm_proj", (T, self.w_in.out_features), torch.float32)
         self.w_in.forward(xn, proj)
         xbc = ctx.scratch("ssm_conv", (T, C), torch.float32)
-        kernels.causal_conv(proj, inner, self.conv, self.conv_bias, state, H * N * P, ctx.row_req, ctx.seg_start,
+        kernels.causal_conv(proj, inner, self.conv, self.conv_bias, state, self.state_offset + H * N * P, ctx.row_req, ctx.seg_start,
                             ctx.seg_len, ctx.state_slots, xbc)
         y = ctx.scratch("ssm_out", (T, inner), torch.float32)
         # q = C, k = B, v = x; a and b from the step size
-        kernels.linear_scan(xbc, inner + G * N, xbc, inner, xbc, 0, H, H // G, N, P, False, state, 0, ctx.seg_start,
+        kernels.linear_scan(xbc, inner + G * N, xbc, inner, xbc, 0, H, H // G, N, P, False, state, self.state_offset, ctx.seg_start,
                             ctx.seg_len, ctx.state_slots, y, dt=proj, dt_offset=inner + C, dt_bias=self.dt_bias,
                             a_log=self.a_log, skip=self.skip, **_scan_workspaces(ctx, T, H, N, P))
         yn = ctx.scratch("ssm_normed", (T, inner), self.dtype)
@@ -185,31 +190,128 @@ class StateSpaceMixer:
         self.w_o.forward(yn, x, accumulate=True, then=then)
 
 
+@register_mixer("gated_linear_attention")
+class GatedLinearAttentionMixer:
+    """Linear attention whose memory fades by a factor of its own per key channel and token. With u the input row:
+    q = c Wq u (c = ``query_scale``), k = Wk u (H heads of dk), v = Wv u (H heads of dv); z = W2 (W1 u) + b (a product
+    through ``decay_rank`` values) gives alpha = sigmoid(z)^(1 / ``tau``) per head and key channel;
+    M_t = diag(alpha_t) M_(t-1) + k_t (x) v_t  (a dk x dv matrix per head);  y_t = M_t^T q_t.
+    Each head's y is brought to unit RMS over its dv values, weighted by ``norm`` [dv] (one weight for all heads), all
+    heads side by side are multiplied by SiLU(Wg u) and sent through ``w_o``. alpha, the recurrence and its state are
+    32-bit; W1 u is handed to the second product in the compute dtype.
+
+    Params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``tau``, ``norm_eps`` and optionally ``decay_rank``
+    (as ``w_a1`` has rows when absent), ``query_scale`` (key_dim^-0.5) and ``out_scale``. Weights: ``w_in`` [(2 H dk + 2 H dv), hidden] (rows of Wq, Wk, Wv, Wg
+    in this order), ``w_a1`` [rank, hidden], ``w_a2`` [H dk, rank], ``a2_bias`` [H dk], ``norm`` [dv], ``w_o`` [hidden, H dv]."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, build):
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads, self.dk, self.dv = int(params["num_heads"]), int(params["key_dim"]), int(params["value_dim"])
+        # the rank of the decay's projection: given, or as the weights' shapes say
+        self.tau, self.rank = float(params["tau"]), int(params.get("decay_rank") or weights["w_a1"].shape[0])
+        self.eps = float(params["norm_eps"])
+        self.q_scale = float(params.get("query_scale", self.dk ** -0.5))
+        self.out_scale = float(params.get("out_scale", 1.0))
+        if not self.tau > 0:
+            raise ValueError("gated linear attention: tau must be positive")
+        if self.dk > 256:
+            raise ValueError(f"gated linear attention: key size {self.dk} exceeds what the recurrence kernel holds (256)")
+        H, dk, dv, D = self.num_heads, self.dk, self.dv, self.hidden_size
+        for name, shape in (("w_in", (2 * H * dk + 2 * H * dv, D)), ("w_a1", (self.rank, D)), ("w_a2", (H * dk, self.rank)),
+                            ("w_o", (D, H * dv))):
+            if tuple(weights[name].shape) != shape:
+                raise ValueError(f"gated linear attention: {name} has shape {tuple(weights[name].shape)}, expected {shape}")
+        self.w_in = Linear(weights["w_in"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_a1 = Linear(weights["w_a1"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_a2 = Linear(weights["w_a2"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.a2_bias = _vector(weights, "a2_bias", H * dk, build, "gated linear attention")
+        self.norm = _vector(weights, "norm", dv, build, "gated linear attention").repeat(H).contiguous()
+        self.dtype = build.compute_dtype
+        self.state_offset = 0
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.num_heads * self.dk * self.dv,), "float32")
+
+    def launch_key(self, ctx, run):
+        return (run.cache_layer, ctx.n_requests)
+
+    takes_then = True
+
+    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
+        T = xn.shape[0]
+        H, dk, dv = self.num_heads, self.dk, self.dv
+        proj = ctx.scratch("gla_proj", (T, self.w_in.out_features), torch.float32)
+        self.w_in.forward(xn, proj)
+        low = ctx.scratch("gla_decay_low", (T, self.rank), self.dtype)
+        self.w_a1.forward(xn, low)
+        z = ctx.scratch("gla_decay_z", (T, H * dk), torch.float32)
+        self.w_a2.forward(low, z)
+        o = ctx.scratch("gla_out", (T, H * dv), torch.float32)
+        kernels.linear_scan(proj, 0, proj, H * dk, proj, 2 * H * dk, H, 1, dk, dv, False, ctx.state(run.cache_layer),
+                            self.state_offset, ctx.seg_start, ctx.seg_len, ctx.state_slots, o, row_gate=z,
+                            row_gate_bias=self.a2_bias, tau=self.tau, q_scale=self.q_scale,
+                            **_scan_workspaces(ctx, T, H, dk, dv, row_decays=True))
+        y = ctx.scratch("gla_normed", (T, H * dv), self.dtype)
+        kernels.gated_group_norm(o, proj, 2 * H * dk + H * dv, self.norm, y, H, self.eps, gate_first=False, gate_act="silu",
+                                 out_scale=self.out_scale)
+        self.w_o.forward(y, x, accumulate=True, then=then)
+
+
 @register_mixer("parallel")
 class ParallelMixer:
-    """Several mixers side by side on the same input: x += sum_i scale_i * mixer_i(xn). Params: ``branches``,
-    a list of (name, PartSpec, scale); branch ``name`` is built from the weights under ``<name>.`` with its
-    scale as ``out_scale``. At most one branch may keep pages and at most one may keep state."""
+    """Several mixers side by side on the same input. ``combine`` "sum" (the default): x += sum_i scale_i * mixer_i(xn).
+    ``combine`` "mean_normed": every branch's output is first brought to unit RMS over the model width and weighted by
+    its own ``<name>_out`` [hidden] (eps ``combine_eps``), and x += (1 / n) sum_i of these. Params: ``branches``, a list of
+    (name, PartSpec, scale); branch ``name`` is built from the weights under ``<name>.`` with its scale as ``out_scale``.
+    At most one branch may keep pages; the states of branches that keep one lie behind one another in the layer's slot."""
 
     def __init__(self, params, weights, build):
         from ..config import PartSpec
         from .registry import MIXERS, build_part, sub_weights
         self.branches = []
+        self.combine = params.get("combine", "sum")
+        if self.combine not in ("sum", "mean_normed"):
+            raise ValueError(f"parallel mixer: unknown way to combine the branches '{self.combine}'")
         for name, spec, scale in params["branches"]:
             spec = PartSpec(spec.kind, dict(spec.params, out_scale=float(scale)))
             self.branches.append((name, build_part(MIXERS, "mixer", spec, sub_weights(weights, name + "."), build)))
-        if sum(m.cache_need() is not None for _, m in self.branches) > 1 or \
-                sum(m.state_need() is not None for _, m in self.branches) > 1:
-            raise ValueError("parallel mixer: at most one branch may keep pages and at most one may keep state")
+        if sum(m.cache_need() is not None for _, m in self.branches) > 1:
+            raise ValueError("parallel mixer: at most one branch may keep pages")
+        self._state_size = 0
+        for name, m in self.branches:
+            need = m.state_need()
+            if need is None:
+                continue
+            if need.dtype != "float32" or len(need.shape) != 1 or not hasattr(m, "state_offset"):
+                raise ValueError(f"parallel mixer: the state of branch '{name}' cannot be laid behind another's")
+            m.state_offset = self._state_size
+            self._state_size += (need.shape[0] + 3) // 4 * 4          # every branch's state starts on 16 bytes
         for name, m in self.branches:
             setattr(self, name, m)
         self.graph_safe = all(getattr(m, "graph_safe", False) for _, m in self.branches)
+        self.out_norms = None
+        if self.combine == "mean_normed":
+            self.eps = float(params["combine_eps"])
+            self.hidden_size = int(params["hidden_size"])
+            self.out_norms = []
+            for name, _ in self.branches:
+                w = weights[name + "_out"]
+                if tuple(w.shape) != (self.hidden_size,):
+                    raise ValueError(f"parallel mixer: {name}_out has shape {tuple(w.shape)}, expected ({self.hidden_size},)")
+                # the mean's factor goes into the weight once, in 32-bit
+                self.out_norms.append((w.to(device=build.device, dtype=torch.float32) / len(self.branches)).contiguous())
 
     def cache_need(self):
         return next((m.cache_need() for _, m in self.branches if m.cache_need() is not None), None)
 
     def state_need(self):
-        return next((m.state_need() for _, m in self.branches if m.state_need() is not None), None)
+        return StateNeed((self._state_size,), "float32") if self._state_size else None
 
     def launch_key(self, ctx, run):
         key = ()
@@ -219,11 +321,33 @@ class ParallelMixer:
             if k is None:
                 return None
             key += tuple(k)
+        if self.combine == "mean_normed":
+            key += (self._sums_clear(ctx),)
         return key
 
     takes_then = True
 
+    def _sums_clear(self, ctx) -> bool:
+        """Whether the branches' own sums are known to be zero (the mixer of this kind that ran before left them so)."""
+        carry = getattr(ctx, "carry", None)
+        return bool(carry is not None and carry.get("parallel_branch_sums") == len(self.branches))
+
     def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
+        if self.combine == "mean_normed":
+            # every branch adds into a sum of its own, which the combining kernel norms, adds to x and clears again
+            T = xn.shape[0]
+            clear = self._sums_clear(ctx)
+            sums = [ctx.scratch(f"parallel_branch_{i}", (T, self.hidden_size), torch.float32) for i in range(len(self.branches))]
+            for (_, m), own in zip(self.branches, sums):
+                if not clear:
+                    kernels.scale_cast(x, own, None, 0.0)
+                m.forward(ctx, run, xn, own)
+            for own, w in zip(sums, self.out_norms):
+                kernels.add_normed(own, w, x, self.eps, clear_y=True)
+            carry = getattr(ctx, "carry", None)
+            if carry is not None:
+                carry["parallel_branch_sums"] = len(self.branches)
+            return
         for i, (_, m) in enumerate(self.branches):
             last = i == len(self.branches) - 1
             if last and then is not None and getattr(m, "takes_then", False):

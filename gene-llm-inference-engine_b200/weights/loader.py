@@ -62,7 +62,7 @@ def read_tensors(path: str, plan: WeightPlan) -> Dict[str, torch.Tensor]:
             if e is None:
                 missing.append(r.name)
                 continue
-            if tuple(e.shape) != tuple(r.shape):
+            if len(e.shape) != len(r.shape) or any(want >= 0 and got != want for got, want in zip(e.shape, r.shape)):
                 wrong.append(f"'{r.name}' has shape {list(e.shape)}, expected {list(r.shape)}")
             elif r.kind == "table" and e.dtype_name not in _INTS:
                 wrong.append(f"'{r.name}' has dtype {e.dtype_name}, expected an integer type")

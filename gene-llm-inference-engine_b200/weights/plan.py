@@ -16,7 +16,7 @@ import torch
 @dataclass(frozen=True)
 class TensorRule:
     name: str
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]   # an extent of -1 is left open: whatever the checkpoint has there is taken
     kind: str = "matrix"     # "matrix", "vector" (norm weights and the like) or "table" (integers)
     # how random weights are drawn for this tensor, when not as its kind says: (mean, std) of a normal
     # distribution, or ("uniform", low, high)
@@ -273,6 +273,93 @@ def pinorax_weight_plan(cfg) -> WeightPlan:
                 if f.shared_ff:
                     out[b + "shared.w_gate_up"] = _cat([t[a + "shared.gate"], t[a + "shared.up"]])
                     out[b + "shared.w_down"] = t[a + "shared.down"]
+        return out
+
+    return WeightPlan(rules, [], assemble)
+
+
+def fovezen_weight_plan(cfg) -> WeightPlan:
+    """Tensor names and shapes of a Fovezen checkpoint: ``embed``, ``head``, ``final.norm`` and, for layer i, ``l<i>.norm1`` /
+    ``l<i>.norm2``, with ``streams`` also ``l<i>.hc1.in`` / ``.out`` / ``.mix`` (and ``hc2`` with a feed-forward), the mixer's
+    tensors under ``l<i>.mix.`` (a parallel mixer: under ``.left.`` and ``.right.``, with ``left.out`` and ``right.out``) and the
+    feed-forward's under ``l<i>.mlp.``. Projections that read the same input become one product: [q; k; v] of an attention
+    (their three convolutions likewise one), [q; k; v; g] of the gated linear attention, [gate; up] of the feed-forward. A
+    model without ``streams`` runs the same block with one copy and unit weights."""
+    D, V, S = cfg.width, cfg.vocab, cfg.streams
+    zero = (0.0, 0.05)                   # the layers' norm weights are stored around zero
+    rules = [TensorRule("embed", (V, D)), TensorRule("head", (V, D)), TensorRule("final.norm", (D,), "vector", zero)]
+    for i, layer in enumerate(cfg.layers):
+        p, m = f"l{i}.", layer.mixer
+        rules.append(TensorRule(p + "norm1", (D,), "vector", zero))
+        q = p + "mix."
+        if layer.type == "attention":
+            rules += [TensorRule(q + "q", (m.heads * m.dim, D)), TensorRule(q + "k", (m.kv_heads * m.dim, D)),
+                      TensorRule(q + "v", (m.kv_heads * m.vdim, D)), TensorRule(q + "q.norm", (m.heads * m.dim,), "vector"),
+                      TensorRule(q + "k.norm", (m.kv_heads * m.dim,), "vector"), TensorRule(q + "o", (D, m.heads * m.vdim))]
+        elif layer.type == "mamba2":
+            rules += [TensorRule(q + "in", (2 * m.inner + 2 * m.groups * m.state + m.heads, D)),
+                      TensorRule(q + "conv", (m.conv_channels, m.conv), "vector", (0.0, 0.4)),
+                      TensorRule(q + "conv.b", (m.conv_channels,), "vector", (0.0, 0.1)),
+                      TensorRule(q + "dt_bias", (m.heads,), "vector", ("uniform", -3.0, 0.5)),
+                      TensorRule(q + "A_log", (m.heads,), "vector", ("uniform", -1.5, 1.0)),
+                      TensorRule(q + "D", (m.heads,), "vector", (1.0, 0.2)),
+                      TensorRule(q + "norm", (m.inner,), "vector"), TensorRule(q + "o", (D, m.inner))]
+        else:
+            a, g = m.left, m.right
+            q = p + "mix.left."
+            for name, rows in (("q", a.heads * a.dim), ("k", a.kv_heads * a.dim), ("v", a.kv_heads * a.vdim)):
+                rules.append(TensorRule(q + name, (rows, D)))
+                if a.conv > 1:
+                    rules.append(TensorRule(q + name + ".conv", (rows, a.conv), "vector", (0.0, 0.5)))
+            rules += [TensorRule(q + "q.norm", (a.dim,), "vector"), TensorRule(q + "k.norm", (a.dim,), "vector"),
+                      TensorRule(q + "o", (D, a.heads * a.vdim))]
+            q = p + "mix.right."
+            rank = g.rank or -1
+            rules += [TensorRule(q + "q", (g.heads * g.dim, D)), TensorRule(q + "k", (g.heads * g.dim, D)),
+                      TensorRule(q + "v", (g.heads * g.vdim, D)), TensorRule(q + "g", (g.heads * g.vdim, D)),
+                      TensorRule(q + "o", (D, g.heads * g.vdim)), TensorRule(q + "norm", (g.vdim,), "vector"),
+                      TensorRule(q + "a1", (rank, D)), TensorRule(q + "a2", (g.heads * g.dim, rank), "matrix", (0.0, 0.3)),
+                      TensorRule(q + "a2.b", (g.heads * g.dim,), "vector", ("uniform", 1.0, 5.0)),
+                      TensorRule(p + "mix.left.out", (D,), "vector"), TensorRule(p + "mix.right.out", (D,), "vector")]
+        if layer.ff is not None:
+            rules += [TensorRule(p + "norm2", (D,), "vector", zero), TensorRule(p + "mlp.gate", (layer.ff, D)),
+                      TensorRule(p + "mlp.up", (layer.ff, D)), TensorRule(p + "mlp.down", (D, layer.ff))]
+        if S is not None:
+            for c in ("hc1.", "hc2.") if layer.ff is not None else ("hc1.",):
+                rules += [TensorRule(p + c + "in", (S,), "vector", (1.0 / S, 0.2)), TensorRule(p + c + "out", (S,), "vector", (1.0, 0.3)),
+                          TensorRule(p + c + "mix", (S, S), "vector", (1.0 / S, 0.3))]
+
+    def assemble(t: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {"embedding.weight": t["embed"], "head.weight": t["head"], "final_norm.weight": t["final.norm"]}
+        for i, layer in enumerate(cfg.layers):
+            p, q = f"l{i}.", f"layers.{i}."
+            out[q + "mixer_norm.weight"] = t[p + "norm1"]
+            a, b = p + "mix.", q + "mixer."
+            if layer.type == "attention":
+                out[b + "w_qkv"] = _cat([t[a + "q"], t[a + "k"], t[a + "v"]])
+                out[b + "q_norm"], out[b + "k_norm"], out[b + "w_o"] = t[a + "q.norm"], t[a + "k.norm"], t[a + "o"]
+            elif layer.type == "mamba2":
+                out[b + "w_in"], out[b + "w_o"], out[b + "norm"] = t[a + "in"], t[a + "o"], t[a + "norm"]
+                out[b + "conv"], out[b + "conv_bias"] = t[a + "conv"], t[a + "conv.b"]
+                out[b + "dt_bias"], out[b + "a_log"], out[b + "skip"] = t[a + "dt_bias"], t[a + "A_log"], t[a + "D"]
+            else:
+                a, b = p + "mix.left.", q + "mixer.left."
+                out[b + "w_qkv"] = _cat([t[a + "q"], t[a + "k"], t[a + "v"]])
+                if layer.mixer.left.conv > 1:
+                    out[b + "conv"] = _cat([t[a + "q.conv"], t[a + "k.conv"], t[a + "v.conv"]])
+                out[b + "q_norm"], out[b + "k_norm"], out[b + "w_o"] = t[a + "q.norm"], t[a + "k.norm"], t[a + "o"]
+                a, b = p + "mix.right.", q + "mixer.right."
+                out[b + "w_in"] = _cat([t[a + "q"], t[a + "k"], t[a + "v"], t[a + "g"]])
+                out[b + "w_a1"], out[b + "w_a2"], out[b + "a2_bias"] = t[a + "a1"], t[a + "a2"], t[a + "a2.b"]
+                out[b + "norm"], out[b + "w_o"] = t[a + "norm"], t[a + "o"]
+                out[q + "mixer.left_out"], out[q + "mixer.right_out"] = t[p + "mix.left.out"], t[p + "mix.right.out"]
+            if layer.ff is not None:
+                out[q + "feed_forward_norm.weight"] = t[p + "norm2"]
+                out[q + "feed_forward.w_gate_up"] = _cat([t[p + "mlp.gate"], t[p + "mlp.up"]])
+                out[q + "feed_forward.w_down"] = t[p + "mlp.down"]
+            for c in ("hc1.", "hc2.") if layer.ff is not None else ("hc1.",):
+                for name, shape in (("in", (1,)), ("out", (1,)), ("mix", (1, 1))):
+                    out[q + c + name] = t[p + c + name] if S is not None else torch.ones(shape, dtype=torch.float32)
         return out
 
     return WeightPlan(rules, [], assemble)

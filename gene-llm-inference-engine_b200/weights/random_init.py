@@ -43,6 +43,8 @@ def write_random_model(config_json: Dict[str, Any], seed: int, out_dir: str, dty
             g = torch.Generator(device="cpu")
             g.manual_seed(_tensor_seed(seed, rule.name))
             init = getattr(rule, "init", None)
+            if any(n < 0 for n in rule.shape):
+                raise ValueError(f"random weights: the configuration leaves a size of '{rule.name}' open")
             if rule.kind == "table":
                 if init is not None and init[0] == "distinct":      # every row: different indices below init[1], in random order
                     order = torch.rand((rule.shape[0], init[1]), generator=g).argsort(dim=1)
