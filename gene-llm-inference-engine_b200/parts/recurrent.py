@@ -322,22 +322,25 @@ class ParallelMixer:
                 return None
             key += tuple(k)
         if self.combine == "mean_normed":
-            key += (self._sums_clear(ctx),)
+            key += (self._sums_clear(ctx, self._sums(ctx, ctx.n_tokens)),)
         return key
 
     takes_then = True
 
-    def _sums_clear(self, ctx) -> bool:
-        """Whether the branches' own sums are known to be zero (the mixer of this kind that ran before left them so)."""
+    def _sums(self, ctx, T: int):
+        return [ctx.scratch(f"parallel_branch_{i}", (T, self.hidden_size), torch.float32) for i in range(len(self.branches))]
+
+    def _sums_clear(self, ctx, sums) -> bool:
+        """Whether the branches' own sums are known to be zero (the mixer of this kind that ran before in this step left these
+        very buffers so)."""
         carry = getattr(ctx, "carry", None)
-        return bool(carry is not None and carry.get("parallel_branch_sums") == len(self.branches))
+        return bool(carry is not None and carry.get("parallel_branch_sums") == tuple(t.data_ptr() for t in sums))
 
     def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
         if self.combine == "mean_normed":
             # every branch adds into a sum of its own, which the combining kernel norms, adds to x and clears again
-            T = xn.shape[0]
-            clear = self._sums_clear(ctx)
-            sums = [ctx.scratch(f"parallel_branch_{i}", (T, self.hidden_size), torch.float32) for i in range(len(self.branches))]
+            sums = self._sums(ctx, xn.shape[0])
+            clear = self._sums_clear(ctx, sums)
             for (_, m), own in zip(self.branches, sums):
                 if not clear:
                     kernels.scale_cast(x, own, None, 0.0)
@@ -346,7 +349,7 @@ class ParallelMixer:
                 kernels.add_normed(own, w, x, self.eps, clear_y=True)
             carry = getattr(ctx, "carry", None)
             if carry is not None:
-                carry["parallel_branch_sums"] = len(self.branches)
+                carry["parallel_branch_sums"] = tuple(t.data_ptr() for t in sums)
             return
         for i, (_, m) in enumerate(self.branches):
             last = i == len(self.branches) - 1
