@@ -8,6 +8,7 @@
     python bench.py --scenario nipadra               (the Nipadra design beside Llama at equal layer sizes, see run_nipadra)
     python bench.py --scenario gekupel               (the Gekupel design beside Llama at equal layer sizes, see run_gekupel)
     python bench.py --scenario pinorax               (the Pinorax design beside Gekupel and Llama at equal layer sizes, see run_pinorax)
+    python bench.py --scenario fovezen               (the Fovezen design beside Nipadra and Llama at equal layer sizes, see run_fovezen)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -1014,6 +1015,214 @@ def run_pinorax(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- Fovezen beside Nipadra
+def fovezen_config(width, ff, layers, vocab, heads, head_dim, kv_heads, window):
+    """A Fovezen model with the layer sizes of a Llama shape, two copies of the stream, every layer with the same
+    feed-forward. Layers in turn: the parallel pair (windowed attention with Llama's heads, three taps and soft-capped
+    scores, beside gated linear attention with heads of 64 x 128), attention over all keys with half a head rotated,
+    the state-space mixer (heads of 64, state 128), the parallel pair again."""
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "mask": {"size": window}, "conv": 3,
+                 "softcap": 30.0, "scale": head_dim ** -0.5},
+        "right": {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16}}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                                          "rot": {"base": 500000.0, "dims": head_dim // 2,
+                                                  "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    ssm = {"type": "mamba2", "mixer": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    kinds = [par, att, ssm, par]
+    return {"architecture": "Fovezen", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "streams": 2, "logit_scale": 0.5,
+            "layers": [dict(kinds[i % 4], mlp={"ff": ff, "kind": "dense", "limit": 7.0}) for i in range(layers)]}
+
+
+def fovezen_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
+    """Each kernel that the design added or changed, alone, beside the like kernel of the Nipadra or Llama path, at the
+    sizes of one layer: a prompt portion of ``T`` tokens of one request and a decode step of 8 requests at a context of
+    ``T``. ``frac`` is the time the kernel's algorithmic bytes (or, where larger, its multiply-adds on the tensor cores) need
+    at the measured peaks, divided by the time it took; ``frac_of_32bit_issue`` the same against the CUDA cores' 32-bit
+    rate, for kernels whose arithmetic has to stay 32-bit."""
+    import torch
+    from geneinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    props = torch.cuda.get_device_properties(dev)
+    simt_ops = props.multi_processor_count * 128 * 1.965e9
+    bf = torch.bfloat16
+
+    def add(name, like, fn, nbytes, flops=0.0, simt=0.0):
+        ms = time_calls(fn, flush=flush)
+        ideal = max(nbytes / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e3
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1), "frac": round(ideal / ms, 3)}
+        if simt:
+            row["frac_of_32bit_issue"] = round(simt / simt_ops * 1e3 / ms, 3)
+        rows.append(row)
+
+    D, page, S = width, 16, 2
+    for what, R, n in (("prefill", 1, T), ("decode", 8, 1)):
+        N = R * n
+        i32 = dict(dtype=torch.int32, device=dev)
+        s0, sl, slots = torch.arange(R, **i32) * n, torch.full((R,), n, **i32), torch.arange(R, **i32)
+        rr = torch.arange(R, **i32).repeat_interleave(n)
+        # the copies of the stream: rewrite + next read in one pass, beside the norm kernels of the other designs
+        X, y = torch.randn(N, S, D, device=dev), torch.randn(N, D, device=dev)
+        xn = torch.empty(N, D, dtype=bf, device=dev)
+        w = torch.ones(D, device=dev)
+        mix, ow, iw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.full((S,), 0.5, device=dev)
+        add(f"streams: rewrite of 2 copies + next read ({what})", "residual_norm",
+            lambda: K.streams(X, y=y, clear_y=True, mix=mix, out_w=ow, in_w=iw, norm_weight=w, eps=1e-6, xn_out=xn), N * D * (S * 8 + 8 + 2))
+        acc, xo = torch.empty(N, D, device=dev), torch.empty(N, D, device=dev)
+        add(f"residual_norm, Nipadra ({what})", "", lambda: K.residual_norm(y, w, xo, 1e-6, 2.0, acc_out=acc, xn_out=xn), N * D * 14)
+        add(f"rmsnorm, Llama ({what})", "", lambda: K.rmsnorm(y, w, xn, 1e-6), N * D * 6)
+        add(f"add_normed, a branch's output into the sum ({what})", "rmsnorm", lambda: K.add_normed(y, w, xo, 1e-6, clear_y=True), N * D * 16)
+        # gated linear attention: heads of 64 x 128
+        H, dk, dv = D // 128, 64, 128
+        proj = torch.randn(N, 2 * H * dk + 2 * H * dv, device=dev) * 0.5
+        z = torch.randn(N, H * dk, device=dev) + 3.0
+        zb = torch.zeros(H * dk, device=dev)
+        out = torch.empty(N, H * dv, device=dev)
+        state = torch.zeros(R, H * dk * dv, device=dev)
+        parts, parts_c = {}, {}
+        if N > K.SCAN_PART:
+            ws = torch.empty(K.scan_parts(N, R), H * dk * dv, device=dev)
+            parts = {"part_len": K.SCAN_PART, "ws_state": ws, "ws_decay": torch.empty(N, H * dk, device=dev)}
+            parts_c = {"part_len": K.SCAN_PART, "ws_state": ws, "ws_decay": torch.empty(N, H, device=dev)}
+        scan_bytes = N * (2 * H * dk + 2 * H * dv) * 4 + 2 * R * H * dk * dv * 4
+        macs = N * H * dk * dv * (4.0 if parts else 3.0)
+        add(f"linear_scan, a decay per row ({what})", "linear_scan", lambda: K.linear_scan(
+            proj, 0, proj, H * dk, proj, 2 * H * dk, H, 1, dk, dv, False, state, 0, s0, sl, slots, out, row_gate=z, row_gate_bias=zb,
+            tau=16.0, q_scale=0.125, **parts), scan_bytes + N * H * dk * 4, simt=macs)
+        decay = torch.full((H,), 0.99, device=dev)
+        add(f"linear_scan, constant decay, Nipadra ({what})", "", lambda: K.linear_scan(
+            proj, 0, proj, H * dk, proj, 2 * H * dk, H, 1, dk, dv, True, state, 0, s0, sl, slots, out, decay=decay, **parts_c), scan_bytes,
+            simt=macs)
+        yb = torch.empty(N, H * dv, dtype=bf, device=dev)
+        nw = torch.ones(H * dv, device=dev)
+        add(f"gated_group_norm per head, SiLU gate after ({what})", "gated_group_norm",
+            lambda: K.gated_group_norm(out, proj, 2 * H * dk + H * dv, nw, yb, H, 1e-6, False, gate_act="silu"), N * H * dv * 10)
+        add(f"gated_group_norm, Nipadra ({what})", "", lambda: K.gated_group_norm(out, proj, 2 * H * dk + H * dv, nw, yb, 1, 1e-6, False),
+            N * H * dv * 10)
+        # windowed attention: convolution of [q; k; v], norm + store, attention with soft-capped scores
+        C = (heads + 2 * kv_heads) * head_dim
+        qkv = torch.randn(N, C, device=dev)
+        cw = torch.randn(C, 3, device=dev) * 0.3
+        st = torch.zeros(R, 2 * C, device=dev)
+        mixed = torch.empty(N, C, device=dev)
+        add(f"causal_conv of [q; k; v], no bias or activation ({what})", "causal_conv",
+            lambda: K.causal_conv(qkv, 0, cw, None, st, 0, rr, s0, sl, slots, mixed, activate=False), N * C * 8)
+        cb = torch.zeros(C, device=dev)
+        add(f"causal_conv with bias and SiLU, Nipadra ({what})", "", lambda: K.causal_conv(qkv, 0, cw, cb, st, 0, rr, s0, sl, slots, mixed), N * C * 8)
+        n_pages = R * ((T + page - 1) // page)
+        kc = torch.randn(n_pages, kv_heads, page, head_dim, device=dev).to(bf)
+        vc = torch.randn(n_pages, kv_heads, page, head_dim, device=dev).to(bf)
+        tables = torch.arange(n_pages, **i32).view(R, -1)
+        pos = (torch.arange(n, **i32) + (T - n)).repeat(R)
+        q = torch.empty(N, heads * head_dim, dtype=bf, device=dev)
+        hw = torch.ones(head_dim, device=dev)
+        freq = torch.rand(head_dim // 4, device=dev)
+        store_bytes = N * (C * 4 + C * 2)
+        add(f"norm_rope_store, norm per head, no rotation ({what})", "norm_rope_store", lambda: K.norm_rope_store(
+            qkv, 0, heads * head_dim, (heads + kv_heads) * head_dim, hw, hw, 1e-6, None, False, pos, rr, tables, q, kc, vc, heads, kv_heads,
+            head_dim, page), store_bytes)
+        wq, wk = torch.ones(heads * head_dim, device=dev), torch.ones(kv_heads * head_dim, device=dev)
+        add(f"norm_rope_store, one norm over all heads, half a head rotated ({what})", "norm_rope_store", lambda: K.norm_rope_store(
+            qkv, 0, heads * head_dim, (heads + kv_heads) * head_dim, wq, wk, 1e-6, freq, False, pos, rr, tables, q, kc, vc, heads, kv_heads,
+            head_dim, page, wide_norm=True), store_bytes)
+        fr = torch.rand(head_dim // 2, device=dev)
+        add(f"norm_rope_store, Nipadra ({what})", "", lambda: K.norm_rope_store(
+            qkv, 0, heads * head_dim, heads * head_dim, hw, hw, 1e-6, fr, True, pos, rr, tables, q, kc, vc, heads, kv_heads, head_dim, page),
+            store_bytes)
+        att = torch.empty_like(q)
+        seen = sum(min(window, p + 1) for p in range(T - n, T))
+        att_flops = 4.0 * R * seen * heads * head_dim
+        att_bytes = R * min(T, window + n) * kv_heads * head_dim * 4 + N * heads * head_dim * 4
+
+        class Ctx:                      # what attention_rows_of_step reads of a step
+            row_req, positions, page_size, max_position = rr, pos, page, T
+
+            @staticmethod
+            def scratch(name, shape, dtype, capacity=None):
+                key = (name, tuple(shape), dtype)
+                if key not in Ctx.kept:
+                    Ctx.kept[key] = torch.empty(shape, dtype=dtype, device=dev)
+                return Ctx.kept[key]
+
+            @staticmethod
+            def attention_work(per_tile):
+                if n == 1:
+                    return torch.arange(R, **i32), torch.zeros((0, 3), **i32), T
+                tiles = [(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)]
+                return torch.zeros(0, **i32), torch.tensor(tiles, **i32), 0
+        Ctx.kept = {}
+        add(f"attention_rows, window {window}, soft-capped scores ({what})", "attention", lambda: K.attention_rows_of_step(
+            Ctx, q, kc, vc, att, tables, heads, kv_heads, head_dim, head_dim, head_dim ** -0.5, window, None, None, None, softcap=30.0),
+            att_bytes, att_flops)
+        rows_dec = torch.arange(R, **i32)
+        per_tile = 128 // (heads // kv_heads)
+        work = torch.tensor([(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)][::-1], **i32)
+        chunk = K.attention_chunk_keys()
+        n_chunks = (T + chunk - 1) // chunk
+        part_o = torch.empty(R, heads * n_chunks * head_dim, device=dev)
+        part_ml = torch.empty(R, heads * n_chunks * 2, device=dev)
+        gate = torch.randn(N, heads, device=dev)
+
+        def attend(win, **ep):
+            if n == 1:
+                K.attention_decode(q, kc, vc, att, rows_dec, rr, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, win,
+                                   part_o, part_ml, n_chunks, n_chunks, **ep)
+            else:
+                K.attention_prefill_tc(q, kc, vc, att, work, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, win, **ep)
+        if n > 1:       # prompt portions of the design run here: the tcgen05 kernel with the cap in its softmax pass
+            add(f"attention on tcgen05, window {window}, soft-capped scores ({what})", "attention",
+                lambda: K.attention_prefill_tc(q, kc, vc, att, work, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, window,
+                                               softcap=30.0), att_bytes, att_flops)
+        add(f"window attention with sink and gate, Nipadra ({what})", "", lambda: attend(window, sink=True, gate=gate, gate_offset=0),
+            att_bytes, att_flops)
+    return rows
+
+
+def run_fovezen(args):
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 at context 2,048) throughput of Fovezen models whose
+    layers have the sizes of the Llama-3.2-1B and Llama-3.1-8B shapes (four layers each, random bf16 weights), beside Nipadra
+    (the closest existing design: a windowed attention beside a recurrence, a state-space mixer, linear attention) and Llama
+    models of the same sizes; then every kernel that the design added or changed alone beside its like kernel. One JSON line."""
+    import torch
+    from geneinfer_b200 import Engine
+    from geneinfer_b200.weights import write_random_model
+    pk = peaks()
+    layers = args.layers or 4
+    context, batch, T = 2048, 8, PREFILL_TOKENS
+    models = []
+    for name, base in (("1b", LLAMA_1B), ("8b", LLAMA_8B)):
+        llama = dict(base, num_hidden_layers=layers, tie_word_embeddings=True)
+        shape = (base["hidden_size"], base["intermediate_size"], layers, base["vocab_size"], base["num_attention_heads"], base["head_dim"],
+                 base["num_key_value_heads"], 1024)
+        for arch, cfg in (("Llama", llama), ("Nipadra", nipadra_config(*shape)), ("Fovezen", fovezen_config(*shape))):
+            if arch == "Llama":
+                folder = model_folder(cfg)
+            else:
+                folder = os.path.join(tempfile.gettempdir(), f"geneinfer_bench_{arch.lower()}_{name}_{layers}_{os.getuid()}")
+                if not os.path.isfile(os.path.join(folder, "done")):
+                    write_random_model(cfg, 1, folder, "bfloat16", std=0.02)
+                    open(os.path.join(folder, "done"), "w").close()
+            llm = Engine(folder, dtype="bfloat16", max_seq_len=context, page_size=PAGE, kv_pages=batch * (context // PAGE),
+                         max_running=batch, step_tokens=T, prefix_cache=False)
+            vocab = base["vocab_size"]
+            ms_prefill = time_prefill(llm.steps, T, 2, vocab)
+            ms_decode, _ = time_decode_device(llm.steps, batch, context, args.steps, args.warmup, vocab)
+            llm.steps.check_status()
+            models.append({"model": f"{arch} at the {SHAPES[name][0]} layer sizes, {layers} layers",
+                           "prefill_2048_tok_s": round(T / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                           "decode_b8_ctx2048_tok_s": round(batch / ms_decode * 1e3, 1), "decode_ms_per_step": round(ms_decode, 4),
+                           "weight_gb": round(llm.model.weight_bytes() / 1e9, 3)})
+            del llm
+            torch.cuda.empty_cache()
+    table = fovezen_kernel_table(2048, 32, 8, 64, 1024, T, pk)
+    print(json.dumps({"metric": "Fovezen beside Nipadra and Llama at equal layer sizes (random bf16 weights)", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "steps": args.steps, "warmup": args.warmup, "peaks": pk["source"],
+                      "peak_gb_s": pk["hbm_gbs"], "peak_tflops": pk["bf16_tflops"], "models": models, "kernels": table}))
+    return 0
+
+
 def run_scenario(args):
     """Two workloads through the entry point, beside the default run: ``mixed`` (32 requests with
     prompts of 128 to 4096 random ids and 256 generated tokens each, admitted together, prompts cut
@@ -1224,7 +1433,7 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="precision of a --scenario run (float32: the requests run alone must give identical tokens)")
-    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra", "gekupel", "pinorax"], default="",
+    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra", "gekupel", "pinorax", "fovezen"], default="",
                     help="a workload through the scheduler (mixed, prefix) or decode steps at a grid of sizes, instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -1239,6 +1448,8 @@ def main():
         return run_nipadra(args)
     if args.scenario == "gekupel":
         return run_gekupel(args)
+    if args.scenario == "fovezen":
+        return run_fovezen(args)
     if args.scenario == "pinorax":
         return run_pinorax(args)
     if args.scenario:

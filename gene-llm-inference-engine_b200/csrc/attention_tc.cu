@@ -181,13 +181,25 @@ struct Cfg {
                                          (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
 };
 
-template <int HD, int KEYS>
+// CAP: the scaled score s becomes cap * tanh(s / cap) before the softmax (cap_log2 = cap * log2(e), scale_over_cap =
+// scale / cap); tanh(y) = 1 - 2 / (exp(2 y) + 1), two more trips to the exponential unit a score.
+template <int HD, int KEYS, bool CAP>
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ work, const int* __restrict__ positions,
                             const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
-                            float scale_log2, int window, int* status, const AttEpilogue ep) {
+                            float scale_log2, int window, int* status, const AttEpilogue ep, float cap_log2, float scale_over_cap) {
+    // a raw score in the softmax's scaled log2 domain (a masked score stays -inf)
+    auto to_log2 = [&](float v) -> float {
+        if constexpr (CAP) {
+            const float e = fast_exp2(v * (scale_over_cap * 2.0f * kLog2e));
+            const float t = 1.0f - __fdividef(2.0f, e + 1.0f);
+            return v == -INFINITY ? -INFINITY : cap_log2 * t;
+        } else {
+            return v * scale_log2;
+        }
+    };
     using C = Cfg<HD, KEYS>;
     extern __shared__ __align__(1024) uint8_t smem[];
     if (smem_u32(smem) & 1023u) {                                  // the swizzled tiles need 1024-byte alignment
@@ -372,6 +384,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             // does not see whole is compiled into a pass of its own.
             constexpr bool kEdge = decltype(edge_tag)::value;
             const uint64_t scale2 = pack2(scale_log2, scale_log2), neg_m2 = pack2(-m_use, -m_use);
+            const float cap_arg = scale_over_cap * 2.0f * kLog2e;
             uint64_t sum2 = pack2(0.f, 0.f);
             uint32_t buf[2][32];
             tmem_ld32(tmem_s + lane_addr, buf[0]);
@@ -396,7 +409,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             }
                             mx_all = max3(mx_all, v0, v1);
                         }
-                        last_pass = !__any_sync(0xffffffffu, mx_all * scale_log2 > m_ref + 8.0f);
+                        last_pass = !__any_sync(0xffffffffu, to_log2(mx_all) > m_ref + 8.0f);
                     }
                     if (last_pass) {
                         tc_fence_before();
@@ -413,9 +426,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         if (!(key + 1 >= row_lo && key + 1 <= row_pos)) v1 = -INFINITY;
                     }
                     mx = max3(mx, v0, v1);
-                    const uint64_t x2 = fma2(pack2(v0, v1), scale2, neg_m2);
                     float x0, x1;
-                    unpack2(x2, x0, x1);
+                    if constexpr (CAP) {
+                        const float e0 = fast_exp2(v0 * cap_arg), e1 = fast_exp2(v1 * cap_arg);
+                        x0 = fmaf(cap_log2, 1.0f - __fdividef(2.0f, e0 + 1.0f), -m_use);
+                        x1 = fmaf(cap_log2, 1.0f - __fdividef(2.0f, e1 + 1.0f), -m_use);
+                        if (kEdge) {
+                            if (v0 == -INFINITY) x0 = -INFINITY;
+                            if (v1 == -INFINITY) x1 = -INFINITY;
+                        }
+                    } else {
+                        unpack2(fma2(pack2(v0, v1), scale2, neg_m2), x0, x1);
+                    }
                     const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                     sum2 = add2(sum2, pack2(p0, p1));
                     __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
@@ -451,7 +473,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             float mx = -INFINITY, sum = 0.f;
             tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, i > 0 ? ((i - 1) & 1) : -1, false);
             if (!ok) break;
-            const float m_tile = mx * scale_log2;
+            const float m_tile = to_log2(mx);
             const bool move = m_tile > m_ref + 8.0f;                     // also true for the first visible key (m_ref = -inf)
             if (__any_sync(0xffffffffu, move)) {
                 const float m_new = fmaxf(m_ref, m_tile);
@@ -530,14 +552,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 }
 
-template <int HD, int KEYS>
+template <int HD, int KEYS, bool CAP>
 static int launch(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
                   const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size, float scale,
-                  int window, long long n_pages, int* status, const AttEpilogue ep, cudaStream_t st) {
+                  int window, long long n_pages, int* status, const AttEpilogue ep, float softcap, cudaStream_t st) {
     using C = Cfg<HD, KEYS>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, KEYS, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) { set_error("attention_prefill_tc: %s", cudaGetErrorString(e)); return 1; }
         configured = true;
     }
@@ -549,9 +571,10 @@ static int launch(const void* q, const void* kc, const void* vc, void* out, cons
     if (make_tensor_map_2d(&mv, vc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, 64,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill_tc")) return 1;
     dim3 grid(Hkv, n_work);
-    launch_kernel((attention_prefill_tc_kernel<HD, KEYS>), dim3(grid), dim3(kThreads), C::kSmemBytes, st, mk, mv,
+    launch_kernel((attention_prefill_tc_kernel<HD, KEYS, CAP>), dim3(grid), dim3(kThreads), C::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
-                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status, ep);
+                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status, ep, CAP ? softcap * kLog2e : 0.f,
+                  CAP ? scale / softcap : 0.f);
     return check_launch("attention_prefill_tc");
 }
 
@@ -574,7 +597,7 @@ static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, cons
                                        int n_work, const int* positions, const int* block_tables, int table_stride, int H,
                                        int Hkv, int hd, int page_size, float scale, int window, long long n_pages,
                                        void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale,
-                                       void* stream) {
+                                       float softcap, void* stream) {
     if (n_work == 0) return 0;
     const AttEpilogue ep{sink, gate, gate_ld, gate_off, out_scale};
     GI_REQUIRE(gi_attention_prefill_tc_supported(hd, H, Hkv, page_size), "attention_prefill_tc: shape not supported");
@@ -582,8 +605,10 @@ static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, cons
     GI_REQUIRE(n_work <= 65535, "attention_prefill_tc: %d work items exceed the grid limit 65535", n_work);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define GI_ATC_LAUNCH(HD_, KEYS_)                                                                                          \
-    atc::launch<HD_, KEYS_>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, page_size, \
-                            scale, window, n_pages, static_cast<int*>(status), ep, st)
+    (softcap > 0.f ? atc::launch<HD_, KEYS_, true>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, \
+                                                   page_size, scale, window, n_pages, static_cast<int*>(status), ep, softcap, st)      \
+                   : atc::launch<HD_, KEYS_, false>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, \
+                                                    page_size, scale, window, n_pages, static_cast<int*>(status), ep, 0.f, st))
     // Keys per tile: 128 at head size 64; 64 at head size 128, where a CTA with 128-key tiles needs 192 KB of shared memory
     // and has an SM to itself, while two CTAs with 64-key tiles (112 KB each) overlap one's softmax with the other's
     // MMAs as at head size 64: 642 against 511 TFLOP/s at 8,192 tokens, 374 against 338 at 2,048 (24:8 heads).
@@ -595,6 +620,6 @@ static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, cons
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
 // its arguments in the program (common.cuh).
-extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {
-    return gi::dispatch(gi_attention_prefill_tc_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, stream);
+extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, float softcap, void* stream) {
+    return gi::dispatch(gi_attention_prefill_tc_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, softcap, stream);
 }

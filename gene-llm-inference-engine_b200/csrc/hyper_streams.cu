@@ -73,30 +73,33 @@ streams_kernel(const StreamsArgs p) {
     const size_t row = static_cast<size_t>(blockIdx.x);
     float* X = p.X + row * S * D;
     constexpr int kS = NS ? NS : kMaxStreams;
+    // pieces whose reads are all requested before anything of them is written (fewer with more copies: registers)
+    constexpr int kBatch = kS <= 2 ? 4 : kS <= 4 ? 2 : 1;
     float ss = 0.f;
 
-    // one piece: reads the copies (and y), rewrites them, returns the next sublayer's u
-    auto piece = [&](int d) -> Vals<VEC> {
-        Vals<VEC> old[kS], yy, u, sum;
+    struct In { Vals<VEC> old[kS], yy; };
+    auto read = [&](int d, In& in) {
 #pragma unroll
         for (int s = 0; s < kS; ++s)
-            if (s < S) old[s] = p.single ? (s == 0 ? load_vals<VEC>(p.single + row * D + d) : old[0])
-                                         : load_vals<VEC>(X + static_cast<size_t>(s) * D + d);
-        if (p.y) {
-            yy = load_vals<VEC>(p.y + row * D + d);
-            if (p.clear_y) {
-                Vals<VEC> zero;
+            if (s < S) in.old[s] = p.single ? (s == 0 ? load_vals<VEC>(p.single + row * D + d) : in.old[0])
+                                            : load_vals<VEC>(X + static_cast<size_t>(s) * D + d);
+        if (p.y) in.yy = load_vals<VEC>(p.y + row * D + d);
+    };
+    // rewrites the copies of one piece and returns the next sublayer's u
+    auto write = [&](int d, const In& in) -> Vals<VEC> {
+        Vals<VEC> u, sum;
+        if (p.y && p.clear_y) {
+            Vals<VEC> zero;
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) zero.v[e] = 0.f;
-                store_vals<VEC>(p.y + row * D + d, zero);
-            }
+            for (int e = 0; e < VEC; ++e) zero.v[e] = 0.f;
+            store_vals<VEC>(p.y + row * D + d, zero);
         }
 #pragma unroll
         for (int e = 0; e < VEC; ++e) u.v[e] = sum.v[e] = 0.f;
 #pragma unroll
         for (int t = 0; t < kS; ++t) {
             if (t >= S) continue;
-            Vals<VEC> nw = old[t];
+            Vals<VEC> nw = in.old[t];
             if (p.y) {
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) nw.v[e] = 0.f;
@@ -105,10 +108,10 @@ streams_kernel(const StreamsArgs p) {
                     if (s >= S) continue;
                     const float m = s_mix[s * S + t];
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) nw.v[e] = fmaf(m, old[s].v[e], nw.v[e]);
+                    for (int e = 0; e < VEC; ++e) nw.v[e] = fmaf(m, in.old[s].v[e], nw.v[e]);
                 }
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) nw.v[e] = fmaf(s_out[t], yy.v[e], nw.v[e]);
+                for (int e = 0; e < VEC; ++e) nw.v[e] = fmaf(s_out[t], in.yy.v[e], nw.v[e]);
             }
             if (p.y || p.single) store_vals<VEC>(X + static_cast<size_t>(t) * D + d, nw);
             if (p.in_w) {
@@ -127,11 +130,24 @@ streams_kernel(const StreamsArgs p) {
 
     Vals<VEC> keep[kStreamsKept];
 #pragma unroll
-    for (int i = 0; i < kStreamsKept; ++i) {
-        const int d = (i * 256 + threadIdx.x) * VEC;
-        if (d < D) keep[i] = piece(d);
+    for (int i0 = 0; i0 < kStreamsKept; i0 += kBatch) {
+        In in[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int d = ((i0 + b) * 256 + threadIdx.x) * VEC;
+            if (d < D) read(d, in[b]);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int d = ((i0 + b) * 256 + threadIdx.x) * VEC;
+            if (d < D) keep[i0 + b] = write(d, in[b]);
+        }
     }
-    for (int d = (kStreamsKept * 256 + threadIdx.x) * VEC; d < D; d += 256 * VEC) piece(d);
+    for (int d = (kStreamsKept * 256 + threadIdx.x) * VEC; d < D; d += 256 * VEC) {
+        In in;
+        read(d, in);
+        write(d, in);
+    }
     if (p.in_w == nullptr) return;
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;

@@ -476,6 +476,61 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ g
     }
 }
 
+// The same for groups of at most 512 channels in 16-byte pieces: a warp per (token, group), eight groups a block, no
+// block barrier; a lane keeps its up to four pieces in registers. The sum's order: a lane's chain over its pieces, then
+// the fixed xor tree.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restrict__ gate, int ld_gate, int gate_off,
+                             const float* __restrict__ weight, TOut* __restrict__ out, int W, int groups, float eps,
+                             int mode, float out_scale, long long total_groups) {
+    pdl_prologue();
+    const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (item >= total_groups) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = item / groups;
+    const int grp = static_cast<int>(item % groups);
+    const int n = W / groups;
+    const float4* yr = reinterpret_cast<const float4*>(y + static_cast<size_t>(t) * W + grp * n);
+    const float4* gr = reinterpret_cast<const float4*>(gate + static_cast<size_t>(t) * ld_gate + gate_off + grp * n);
+    const float4* w = reinterpret_cast<const float4*>(weight + grp * n);
+    TOut* o = out + static_cast<size_t>(t) * W + grp * n;
+    float4 kept[4], gk[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = lane + k * 32;
+        kept[k] = gk[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n / 4) {
+            kept[k] = yr[i];
+            gk[k] = gr[i];
+            if (mode == 1) {
+                kept[k].x *= silu_f(gk[k].x); kept[k].y *= silu_f(gk[k].y);
+                kept[k].z *= silu_f(gk[k].z); kept[k].w *= silu_f(gk[k].w);
+            }
+        }
+        ss = fmaf(kept[k].x, kept[k].x, ss); ss = fmaf(kept[k].y, kept[k].y, ss);
+        ss = fmaf(kept[k].z, kept[k].z, ss); ss = fmaf(kept[k].w, kept[k].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = lane + k * 32;
+        if (i >= n / 4) continue;
+        const float4 ww = w[i];
+        float r[4] = {ww.x * (scale * kept[k].x), ww.y * (scale * kept[k].y), ww.z * (scale * kept[k].z), ww.w * (scale * kept[k].w)};
+        if (mode == 0) {
+            r[0] *= 1.0f / (1.0f + expf(-gk[k].x)); r[1] *= 1.0f / (1.0f + expf(-gk[k].y));
+            r[2] *= 1.0f / (1.0f + expf(-gk[k].z)); r[3] *= 1.0f / (1.0f + expf(-gk[k].w));
+        } else if (mode == 2) {
+            r[0] *= silu_f(gk[k].x); r[1] *= silu_f(gk[k].y); r[2] *= silu_f(gk[k].z); r[3] *= silu_f(gk[k].w);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[4 * i + c] = from_float<TOut>(r[c] * out_scale);
+    }
+}
+
 }  // namespace gi
 
 using namespace gi;
@@ -562,6 +617,14 @@ static int gi_gated_group_norm_impl(const float* y, const float* gate, int ld_ga
     const bool vec = n % 4 == 0 && n <= 4096 && W % 4 == 0 && ld_gate % 4 == 0 && gate_off % 4 == 0 &&
                      reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(gate) % 16 == 0 &&
                      reinterpret_cast<uintptr_t>(weight) % 16 == 0;
+    if (vec && n <= 512 && groups > 1 && (out_dtype == kBF16 || out_dtype == kF32)) {
+        // small groups: a warp per group
+        const long long total = static_cast<long long>(T) * groups;
+        const unsigned blocks = static_cast<unsigned>((total + 7) / 8);
+        if (out_dtype == kBF16) launch_kernel((gated_group_norm_warp_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<__nv_bfloat16*>(out), W, groups, eps, mode, out_scale, total);
+        else launch_kernel((gated_group_norm_warp_kernel<float>), dim3(blocks), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<float*>(out), W, groups, eps, mode, out_scale, total);
+        return check_launch("gated_group_norm");
+    }
     if (out_dtype == kBF16) {
         if (vec) launch_kernel((gated_group_norm_kernel<__nv_bfloat16, true>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<__nv_bfloat16*>(out), W, groups, eps, mode, out_scale);
         else launch_kernel((gated_group_norm_kernel<__nv_bfloat16, false>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<__nv_bfloat16*>(out), W, groups, eps, mode, out_scale);

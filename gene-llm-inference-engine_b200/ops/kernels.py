@@ -469,10 +469,11 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[tor
 def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
                            tables: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
                            window: Optional[int], chunk: Optional[int], slopes: Optional[torch.Tensor],
-                           sinks: Optional[torch.Tensor], softcap: Optional[float] = None) -> None:
+                           sinks: Optional[torch.Tensor], softcap: Optional[float] = None, tiles_on=None) -> None:
     """``attention_rows`` for all rows of a step. Over a bfloat16 cache with sizes that the tensor-core form serves, the
     step's single tokens and the tiles of its prompt portions (``ctx.attention_work``) run as two launches, each with its
-    keys cut into ranges when it has few tiles; otherwise one launch works row by row."""
+    keys cut into ranges when it has few tiles; otherwise one launch works row by row. ``tiles_on`` = (tokens per tile,
+    fn(work)): the tiles of prompt portions go to ``fn`` instead, another kernel that serves this form of attention."""
     common = dict(window=window, chunk=chunk, slopes=slopes, sinks=sinks, softcap=softcap)
     per_tile = attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, v_cache is None) \
         if k_cache.dtype is torch.bfloat16 else 0
@@ -481,6 +482,11 @@ def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache:
                        ctx.page_size, scale, **common)
         return
     rows, work, _ = ctx.attention_work(per_tile)
+    if tiles_on is not None:
+        other = ctx.attention_work(tiles_on[0])[1]
+        if other.shape[0]:
+            tiles_on[1](other)
+        work = work[:0]
     span = min(v for v in (window, chunk, getattr(ctx, "max_position", None), 1 << 30) if v)
     for name, lst, n in (("rows", rows, rows.numel()), ("tiles", work, work.shape[0])):
         if n == 0:
@@ -886,9 +892,9 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          work: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
                          num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int],
                          sink: bool = False, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
-                         out_scale: float = 1.0) -> None:
+                         out_scale: float = 1.0, softcap: Optional[float] = None) -> None:
     """Attention of prompt portions on the tcgen05 tensor cores: ``work`` [n, 3] = (first step row of
-    a tile, tokens in it (at most 128 // group size), request index)."""
+    a tile, tokens in it (at most 128 // group size), request index). ``softcap`` c: the scaled score s becomes c tanh(s / c)."""
     if work.dim() != 2 or work.shape[1] != 3:
         raise KernelError("attention_prefill_tc: work must be [n, 3]")
     if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
@@ -901,7 +907,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
         k_cache.shape[0], _tc_state(q.device).status.data_ptr(), *_epilogue(sink, gate, gate_offset, out_scale, num_heads),
-        _stream()), "attention_prefill_tc")
+        float(softcap or 0.0), _stream()), "attention_prefill_tc")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

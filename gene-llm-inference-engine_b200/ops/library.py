@@ -103,7 +103,7 @@ _SIGNATURES = {
     "gi_gemm_tc_cluster_capacity": [c_int, c_int, c_int],
     "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int,
-                                c_float, c_void_p],
+                                c_float, c_float, c_void_p],
     "gi_attention_prefill_tc_supported": [c_int, c_int, c_int, c_int],
     "gi_attention_fast_supported": [c_int, c_int, c_int],
     "gi_attention_generic_supported": [c_int],

@@ -105,6 +105,10 @@ class AttentionMixer:
         if self.extended and getattr(self.position, "cos", None) is not None:
             raise ValueError("attention: with these options the rotation's angles are computed on the device "
                              "(position encoding 'rope_on_device' or 'none')")
+        # soft-capped scores alone (equal key and value sizes, nothing else of the row form): prompt portions may run on the
+        # tcgen05 kernel, which has the cap; single tokens stay on the row-form kernel
+        self.cap_only = (self.softcap is not None and self.value_dim == self.head_dim and self.chunk is None and self.slopes is None
+                         and not self.learned_sink and not params.get("sink") and build.compute_dtype is torch.bfloat16)
         self.q_norm = self.k_norm = None
         if self.qk_norm_eps is not None and not params.get("qk_norm_weights", True):
             self.q_norm = self.k_norm = torch.ones(self.head_dim, dtype=torch.float32, device=build.device)
@@ -177,8 +181,11 @@ class AttentionMixer:
         kernels) how many rows are single decoded tokens, how many tiles the prompt portions make and how many
         chunks the longest context of a single token has. Asking also places this step's work lists on the device."""
         if self.row_form:
-            return (run.cache_layer, run.writes_cache) + kernels.attention_rows_launch_key(
+            key = (run.cache_layer, run.writes_cache) + kernels.attention_rows_launch_key(
                 ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, False, self.dtype)
+            if self._cap_tiles_on_tcgen05(ctx):
+                key += (ctx.attention_work(128 // (self.num_heads // self.num_kv_heads))[1].shape[0],)
+            return key
         if not self._fast_now(ctx):
             return (run.cache_layer, run.writes_cache)
         rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (self.num_heads // self.num_kv_heads))
@@ -186,6 +193,10 @@ class AttentionMixer:
                 (longest + self.chunk_keys - 1) // self.chunk_keys)
 
     takes_then = True      # forward accepts ``then``
+
+    def _cap_tiles_on_tcgen05(self, ctx) -> bool:
+        return (self.cap_only and hasattr(ctx, "attention_work") and self.prefill_on_tcgen05(ctx.page_size)
+                and kernels.attention_rows_tile_tokens(self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, False) > 0)
 
     def _fast_now(self, ctx) -> bool:
         """Whether this step's attention runs on the tensor-core kernels: bfloat16 with a head size they are built for;
@@ -264,8 +275,14 @@ class AttentionMixer:
                                 write_kv=run.writes_cache, value_dim=self.value_dim, wide_norm=self.wide_norm)
         if self.row_form:
             att = ctx.scratch("att", (T, H * self.value_dim), self.dtype)
+            tiles_on = None
+            if self._cap_tiles_on_tcgen05(ctx):
+                tiles_on = (128 // (H // Hkv), lambda work: kernels.attention_prefill_tc(
+                    q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd, ctx.page_size, self.scale, self.window,
+                    softcap=self.softcap))
             kernels.attention_rows_of_step(ctx, q, k_cache, v_cache, att, tables, H, Hkv, hd, self.value_dim, self.scale,
-                                           self.window, self.chunk, self.slopes, self.sink_weight, softcap=self.softcap)
+                                           self.window, self.chunk, self.slopes, self.sink_weight, softcap=self.softcap,
+                                           tiles_on=tiles_on)
             self.w_o.forward(att, x, accumulate=True, then=then)
             return
         att = ctx.scratch("att", (T, H * hd), self.dtype)

@@ -334,7 +334,10 @@ def _left_ctx(part, m, dtype, n, max_len=256, page_size=8):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m", [LEFT, dict(LEFT, heads=2, kv_heads=2, dim=64, vdim=64, conv=2, softcap=None, mask={"size": 5}),
-                               dict(LEFT, heads=4, kv_heads=1, dim=32, vdim=16, conv=None, mask={"size": 300})])
+                               dict(LEFT, heads=4, kv_heads=1, dim=32, vdim=16, conv=None, mask={"size": 300}),
+                               # soft-capped scores at the head sizes whose prompt portions the tcgen05 kernel runs
+                               dict(LEFT, heads=4, kv_heads=2, dim=64, vdim=64, conv=2, softcap=2.5, scale=0.5, mask={"size": 23}),
+                               dict(LEFT, heads=2, kv_heads=1, dim=128, vdim=128, conv=None, softcap=1.5, scale=0.3, mask={"size": 300})])
 @pytest.mark.parametrize("cut", sorted(CUTS))
 def test_window_attention_with_a_convolution_of_its_projections(dtype, m, cut):
     D = 40
