@@ -1171,10 +1171,9 @@ def fovezen_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
                                    part_o, part_ml, n_chunks, n_chunks, **ep)
             else:
                 K.attention_prefill_tc(q, kc, vc, att, work, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, win, **ep)
-        if n > 1:       # prompt portions of the design run here: the tcgen05 kernel with the cap in its softmax pass
-            add(f"attention on tcgen05, window {window}, soft-capped scores ({what})", "attention",
-                lambda: K.attention_prefill_tc(q, kc, vc, att, work, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, window,
-                                               softcap=30.0), att_bytes, att_flops)
+        # where the design's attention runs at these sizes: the tensor-core kernels of plain attention, with the cap in their softmax pass
+        add(f"attention on the tensor cores, window {window}, soft-capped scores ({what})", "attention", lambda: attend(window, softcap=30.0),
+            att_bytes, att_flops)
         add(f"window attention with sink and gate, Nipadra ({what})", "", lambda: attend(window, sink=True, gate=gate, gate_offset=0),
             att_bytes, att_flops)
     return rows

@@ -131,7 +131,13 @@ template <int HD, int TILE, bool TMA, bool kMasked, bool kUpper = true>
 __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint32_t k_tile, uint32_t v_tile, int key0,
                                                const int* row_lo, const int* row_pos, float scale_log2,
                                                float (*o)[4], float* m, float* l, int lane,
-                                               const LaneOffsets<HD, TILE, TMA>& off) {
+                                               const LaneOffsets<HD, TILE, TMA>& off, float cap_log2 = 0.f, float cap_arg = 0.f) {
+    // cap_log2 = c log2(e) > 0: the scaled score s becomes c tanh(s / c), tanh(y) = 1 - 2 / (exp(2 y) + 1) with
+    // cap_arg = 2 log2(e) scale / c; a masked score stays -inf
+    auto to_log2 = [&](float v) -> float {
+        if (cap_log2 == 0.f) return v * scale_log2;
+        return v == -INFINITY ? -INFINITY : cap_log2 * (1.0f - __fdividef(2.0f, exp2f(v * cap_arg) + 1.0f));
+    };
     // kUpper false: rows 8..15 of the tile are padding (a decode tile holds at most 8 query heads);
     // their softmax and rescaling are skipped and their weights enter P V as zeros.
     constexpr int kK = HD / 16;                 // k-steps of Q K^T
@@ -170,7 +176,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
     for (int r = 0; r < kR; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m[r], mx[r] * scale_log2);            // scale > 0: the maximum commutes with it
+        const float m_new = fmaxf(m[r], to_log2(mx[r]));                // scale > 0: the maximum commutes with it (and with the cap)
         corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
         m[r] = m_new;
         m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;                   // a row that has seen no key yet: all weights 0
@@ -181,7 +187,8 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
 #pragma unroll
         for (int e = 0; e < 2 * kR; ++e) {
             const int r = e >> 1;
-            const float p = exp2f(fmaf(s[j][e], scale_log2, -m_use[r]));  // masked scores (-inf) give 0
+            const float p = cap_log2 == 0.f ? exp2f(fmaf(s[j][e], scale_log2, -m_use[r]))      // masked scores (-inf) give 0
+                                            : exp2f(to_log2(s[j][e]) - m_use[r]);
             s[j][e] = p;
             sum[r] += p;
         }
@@ -409,6 +416,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             int max_chunks, int n_chunks, __nv_bfloat16* __restrict__ out, int* status, int stream_kv,
                             const AttEpilogue ep) {
     using Cfg = DecodeTma<HD>;
+    const float cap_log2 = ep.softcap > 0.f ? ep.softcap * kLog2e : 0.f;
+    const float cap_arg = ep.softcap > 0.f ? 2.0f * scale_log2 / ep.softcap : 0.f;
     uint64_t stream_policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_policy));
     constexpr int kTile = Cfg::kTile, kStages = Cfg::kStages;
@@ -592,9 +601,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kv_addr<HD, kTile, true>(v_tile, row, c)), "r"(0) : "memory");
                 }
                 __syncwarp();
-                warp_tile_step<HD, kTile, true, true, WIDE>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                warp_tile_step<HD, kTile, true, true, WIDE>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off, cap_log2, cap_arg);
             } else {
-                warp_tile_step<HD, kTile, true, false, WIDE>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                warp_tile_step<HD, kTile, true, false, WIDE>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off, cap_log2, cap_arg);
             }
             __syncwarp();                                   // every lane is done reading the stage
             if (lane == 0 && tile == ci.tile0) timeline_record(kTlAttentionDecode, 3);
@@ -1149,9 +1158,9 @@ static int gi_attention_decode_impl(const void* q, const void* k_cache, const vo
                                    int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window,
                                    float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages,
                                    void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale,
-                                   void* stream) {
+                                   float softcap, void* stream) {
     if (n_rows == 0) return 0;
-    const AttEpilogue ep{sink, gate, gate_ld, gate_off, out_scale};
+    const AttEpilogue ep{sink, gate, gate_ld, gate_off, out_scale, softcap > 0.f ? softcap : 0.f};
     GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_decode: head size %d with %d/%d heads is not built", hd, H, Hkv);
     GI_REQUIRE(n_chunks >= 1 && n_chunks <= max_chunks, "attention_decode: %d chunks exceed the workspace's %d", n_chunks, max_chunks);
     GI_REQUIRE(n_rows <= 65535 && Hkv <= 65535, "attention_decode: grid too large");
@@ -1172,6 +1181,7 @@ static int gi_attention_decode_impl(const void* q, const void* k_cache, const vo
         }
 #undef GI_DECODE_TMA
     }
+    GI_REQUIRE(!(softcap > 0.f), "attention_decode: soft-capped scores are served for pages that TMA boxes can tile only");
 #define GI_DECODE(HD) return launch_decode<HD>(q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, \
                                                table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, ep, st)
     switch (hd) {
@@ -1219,8 +1229,8 @@ static int gi_attention_prefill_impl(const void* q, const void* k_cache, const v
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
 // its arguments in the program (common.cuh).
-extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows, int n_rows, const int* row_req, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {
-    return gi::dispatch(gi_attention_decode_impl, q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, stream);
+extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows, int n_rows, const int* row_req, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, float softcap, void* stream) {
+    return gi::dispatch(gi_attention_decode_impl, q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, softcap, stream);
 }
 
 extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {

@@ -95,6 +95,7 @@ struct AttEpilogue {
     const float* gate;
     int gate_ld, gate_off;
     float out_scale;
+    float softcap = 0.f;      // c > 0: the scaled score s becomes c tanh(s / c) before the softmax (kernels that say they take it)
     __host__ __device__ bool plain() const { return !sink && gate == nullptr && out_scale == 1.0f; }
 };
 // The factor on the unnormalised output of row (t, h) whose weights are exp2(score - m_log2) and sum to l.

@@ -469,11 +469,12 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[tor
 def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
                            tables: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
                            window: Optional[int], chunk: Optional[int], slopes: Optional[torch.Tensor],
-                           sinks: Optional[torch.Tensor], softcap: Optional[float] = None, tiles_on=None) -> None:
+                           sinks: Optional[torch.Tensor], softcap: Optional[float] = None, tiles_on=None, singles_on=None) -> None:
     """``attention_rows`` for all rows of a step. Over a bfloat16 cache with sizes that the tensor-core form serves, the
     step's single tokens and the tiles of its prompt portions (``ctx.attention_work``) run as two launches, each with its
     keys cut into ranges when it has few tiles; otherwise one launch works row by row. ``tiles_on`` = (tokens per tile,
-    fn(work)): the tiles of prompt portions go to ``fn`` instead, another kernel that serves this form of attention."""
+    fn(work)): the tiles of prompt portions go to ``fn`` instead, another kernel that serves this form of attention;
+    ``singles_on`` = fn(rows, longest context): likewise the rows of requests that bring a single token."""
     common = dict(window=window, chunk=chunk, slopes=slopes, sinks=sinks, softcap=softcap)
     per_tile = attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, v_cache is None) \
         if k_cache.dtype is torch.bfloat16 else 0
@@ -487,6 +488,10 @@ def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache:
         if other.shape[0]:
             tiles_on[1](other)
         work = work[:0]
+    if singles_on is not None:
+        if rows.numel():
+            singles_on(rows, ctx.attention_work(per_tile)[2])
+        rows = rows[:0]
     span = min(v for v in (window, chunk, getattr(ctx, "max_position", None), 1 << 30) if v)
     for name, lst, n in (("rows", rows, rows.numel()), ("tiles", work, work.shape[0])):
         if n == 0:
@@ -837,10 +842,11 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
                      window: Optional[int], part_o: torch.Tensor, part_ml: torch.Tensor, max_chunks: int,
                      n_chunks: int, sink: bool = False, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
-                     out_scale: float = 1.0) -> None:
+                     out_scale: float = 1.0, softcap: Optional[float] = None) -> None:
     """Attention of single decoded tokens (bfloat16): ``rows`` lists their step rows; the context is
     split into fixed chunks whose partial results go through ``part_o`` / ``part_ml``. ``sink``, ``gate``,
-    ``gate_offset``, ``out_scale``: as in ``attention_generic``."""
+    ``gate_offset``, ``out_scale``: as in ``attention_generic``. ``softcap`` c (pages that ``attention_tma_pages`` accepts
+    only): the scaled score s becomes c tanh(s / c)."""
     n = rows.numel()
     if part_o.numel() < n * num_heads * max_chunks * head_dim or part_ml.numel() < n * num_heads * max_chunks * 2:
         raise KernelError("attention_decode: the workspace is too small")
@@ -855,7 +861,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
         _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), max_chunks, n_chunks,
         k_cache.shape[0], _tc_state(q.device).status.data_ptr(), *_epilogue(sink, gate, gate_offset, out_scale, num_heads),
-        _stream()), "attention_decode")
+        float(softcap or 0.0), _stream()), "attention_decode")
     tma = page_size % 8 == 0 and (32 % page_size == 0 or page_size % 32 == 0)
     if n_chunks > 1 or not tma:
         count_launches(1)     # the kernel that merges the chunks (not needed when every context is one chunk)

@@ -106,7 +106,7 @@ class AttentionMixer:
             raise ValueError("attention: with these options the rotation's angles are computed on the device "
                              "(position encoding 'rope_on_device' or 'none')")
         # soft-capped scores alone (equal key and value sizes, nothing else of the row form): prompt portions may run on the
-        # tcgen05 kernel, which has the cap; single tokens stay on the row-form kernel
+        # tcgen05 kernel and single tokens on the decode kernel, which have the cap
         self.cap_only = (self.softcap is not None and self.value_dim == self.head_dim and self.chunk is None and self.slopes is None
                          and not self.learned_sink and not params.get("sink") and build.compute_dtype is torch.bfloat16)
         self.q_norm = self.k_norm = None
@@ -144,7 +144,8 @@ class AttentionMixer:
         self.fast = self.dtype is torch.bfloat16 and not self.row_form and kernels.attention_fast_supported(
             self.head_dim, self.num_heads, self.num_kv_heads)
         self._prefill_rows = {}
-        if self.fast:
+        self.cap_fast = self.cap_only and kernels.attention_fast_supported(self.head_dim, self.num_heads, self.num_kv_heads)
+        if self.fast or self.cap_fast:
             self.chunk_keys = kernels.attention_chunk_keys()
             self.max_chunks = (build.max_position + self.chunk_keys - 1) // self.chunk_keys
 
@@ -185,6 +186,9 @@ class AttentionMixer:
                 ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, False, self.dtype)
             if self._cap_tiles_on_tcgen05(ctx):
                 key += (ctx.attention_work(128 // (self.num_heads // self.num_kv_heads))[1].shape[0],)
+            if self._cap_singles_on_decode(ctx):
+                per_tile = kernels.attention_rows_tile_tokens(self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, False)
+                key += ((ctx.attention_work(per_tile)[2] + self.chunk_keys - 1) // self.chunk_keys,)
             return key
         if not self._fast_now(ctx):
             return (run.cache_layer, run.writes_cache)
@@ -193,6 +197,10 @@ class AttentionMixer:
                 (longest + self.chunk_keys - 1) // self.chunk_keys)
 
     takes_then = True      # forward accepts ``then``
+
+    def _cap_singles_on_decode(self, ctx) -> bool:
+        return (self.cap_fast and hasattr(ctx, "attention_work") and kernels.attention_tma_pages(ctx.page_size)
+                and kernels.attention_rows_tile_tokens(self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, False) > 0)
 
     def _cap_tiles_on_tcgen05(self, ctx) -> bool:
         return (self.cap_only and hasattr(ctx, "attention_work") and self.prefill_on_tcgen05(ctx.page_size)
@@ -280,9 +288,18 @@ class AttentionMixer:
                 tiles_on = (128 // (H // Hkv), lambda work: kernels.attention_prefill_tc(
                     q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd, ctx.page_size, self.scale, self.window,
                     softcap=self.softcap))
+            singles_on = None
+            if self._cap_singles_on_decode(ctx):
+                def singles_on(rows, longest):
+                    n = rows.numel()
+                    part_o = ctx.scratch("att_part_o", (n, H * self.max_chunks * hd), torch.float32, capacity=ctx.max_requests)
+                    part_ml = ctx.scratch("att_part_ml", (n, H * self.max_chunks * 2), torch.float32, capacity=ctx.max_requests)
+                    kernels.attention_decode(q, k_cache, v_cache, att, rows, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                             ctx.page_size, self.scale, self.window, part_o, part_ml, self.max_chunks,
+                                             (longest + self.chunk_keys - 1) // self.chunk_keys, softcap=self.softcap)
             kernels.attention_rows_of_step(ctx, q, k_cache, v_cache, att, tables, H, Hkv, hd, self.value_dim, self.scale,
                                            self.window, self.chunk, self.slopes, self.sink_weight, softcap=self.softcap,
-                                           tiles_on=tiles_on)
+                                           tiles_on=tiles_on, singles_on=singles_on)
             self.w_o.forward(att, x, accumulate=True, then=then)
             return
         att = ctx.scratch("att", (T, H * hd), self.dtype)

@@ -351,7 +351,11 @@ def test_window_attention_with_a_convolution_of_its_projections(dtype, m, cut):
     inputs = [_bf(torch.randn(n, D, generator=g)) for n in (40, 2, 19)]
     rnd = pf.ident if dtype is torch.float32 else pf.bf16
     want = [pf.window_conv_attention(w, "p.", m, x.double(), EPS, F, rnd) for x in inputs]
-    got = _run_mixer(part, _left_ctx(part, m, dtype, 3), inputs, CUTS[cut], dtype, D)
+    ctx = _left_ctx(part, m, dtype, 3)
+    # capped scores alone, at head sizes 64 and 128 in bfloat16: the tensor-core kernels of plain attention take the cap
+    fast = dtype is torch.bfloat16 and m.get("softcap") is not None and m["dim"] == m["vdim"] and m["dim"] in (64, 128)
+    assert part._cap_singles_on_decode(ctx) == fast and part._cap_tiles_on_tcgen05(ctx) == fast
+    got = _run_mixer(part, ctx, inputs, CUTS[cut], dtype, D)
     for r in range(3):
         _close(got[r], want[r], dtype, f"window attention, request {r}, {cut}", b16=3e-2)
 
@@ -791,7 +795,7 @@ def _random_config(seed):
     """A configuration drawn from a seed: sizes, layer order, copies, loop and constants all differ from case to case."""
     import random
     r = random.Random(seed)
-    width = r.choice([64, 72, 96, 160, 176, 256])
+    width = r.choice([64, 72, 96, 160, 176, 256, 320])
     layers = []
 
     def ff():
@@ -801,24 +805,24 @@ def _random_config(seed):
         f, limit = ff()
         if kind == "attention":
             kv = r.choice([1, 2, 3])
-            dim = r.choice([16, 32, 64, 128])
+            dim = r.choice([16, 32, 48, 64, 96, 128])
             dims = r.choice([None, dim, dim // 2, 8])
             scaling = (r.choice([2.0, 8.0]), 1.0, r.choice([2.0, 4.0]), r.choice([16, 64, 2048])) if dims and r.random() < 0.6 else None
-            layers.append(fc.attention(kv * r.choice([1, 2, 4]), kv, dim, r.choice([dim, 16, 48]), r.choice([0.08, 0.125, 0.2]),
+            layers.append(fc.attention(kv * r.choice([1, 2, 4]), kv, dim, r.choice([dim, 16, 48, 80]), r.choice([0.08, 0.125, 0.2]),
                                        rot=None if dims is None else fc.rot(r.choice([100.0, 10000.0, 250000.0]), dims, scaling), ff=f, limit=limit))
         elif kind == "mamba2":
             groups = r.choice([1, 2, 3])
             heads = groups * r.choice([1, 2, 4])
-            vdim = r.choice([8, 16, 24, 64])
+            vdim = r.choice([8, 16, 24, 48, 64])
             ng = r.choice([n for n in (1, 2, heads) if (heads * vdim) % n == 0])
             layers.append(fc.mamba2(heads, vdim, r.choice([8, 16, 48, 100]), groups, r.choice([1, 2, 3, 4]), ng, ff=f, limit=limit))
         else:
             kv = r.choice([1, 2, 4])
-            dim = r.choice([16, 32, 64])
-            layers.append(fc.parallel(fc.left(kv * r.choice([1, 2, 3]), kv, dim, r.choice([dim, 16, 48]), r.choice([0.1, 0.125, 0.3]),
+            dim = r.choice([16, 24, 32, 64, 80, 128])
+            layers.append(fc.parallel(fc.left(kv * r.choice([1, 2, 3]), kv, dim, r.choice([dim, 16, 48, 96]), r.choice([0.1, 0.125, 0.3]),
                                               r.choice([3, 16, 17, 50, 96, 1000]), conv=r.choice([None, 2, 3, 4]), softcap=r.choice([None, 5.0, 30.0])),
-                                      fc.right(r.randint(1, 6), r.choice([8, 16, 32, 72]), r.choice([8, 16, 32, 40]), r.choice([1.0, 4.0, 16.0]),
-                                               r.choice([4, 8, 16, 20])), ff=f, limit=limit))
+                                      fc.right(r.randint(1, 6), r.choice([8, 16, 32, 48, 72, 128]), r.choice([8, 16, 32, 40, 96]), r.choice([1.0, 4.0, 16.0]),
+                                               r.choice([4, 8, 16, 20, 32])), ff=f, limit=limit))
     n = len(layers)
     loop = None
     if r.random() < 0.6:
@@ -828,7 +832,7 @@ def _random_config(seed):
                     logit_scale=r.choice([None, 0.5, 1.7]), loop=loop)
 
 
-@pytest.mark.parametrize("seed", range(10))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("GENEINFER_TEST_SEEDS", "12"))))
 def test_random_configurations_under_a_mixed_trace(seed, tmp_path):
     config = _random_config(seed)
     folder = fc.make_model_dir(config, 100 + seed, str(tmp_path / "m"), std=0.15)
