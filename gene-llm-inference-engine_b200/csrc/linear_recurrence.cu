@@ -109,8 +109,10 @@ __device__ __forceinline__ int parts_before(const ScanArgs& p, int r) {
     return base;
 }
 
+// (Left alone the compiler takes the kernel past 128 registers a thread, with a decay per row to 168, and a launch of a
+// few heads' blocks then needs a second, nearly empty round over the SMs: it is held to 512 threads an SM.)
 template <int kDk, int kRT, bool kParts, bool kRowDecay>
-__global__ void __launch_bounds__(kDk / kRT * 8)
+__global__ void __launch_bounds__(kDk / kRT * 8, (kRowDecay || kDk <= 128) ? 512 / (kDk / kRT * 8) : 1)
 linear_scan_kernel(const ScanArgs p) {
     pdl_prologue();
     // A thread owns kRT rows x 4 columns of the state in registers (thread = row group x column group; a block covers
