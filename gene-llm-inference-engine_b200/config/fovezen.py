@@ -9,7 +9,7 @@ for none; ``kind`` "dense" with ``ff`` and ``limit``). Mixer types:
 * "attention": ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale`` and optionally ``rot`` (``base``, ``dims`` and optionally
   ``scaling`` with ``factor``, ``low``, ``high``, ``original``);
 * "mamba2": ``heads``, ``vdim``, ``state``, ``groups``, ``conv``, ``norm_groups``;
-* "parallel": ``left`` (``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``mask.size`` and optionally ``conv`` and
+* "parallel": ``left`` (``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale`` and optionally ``mask.size``, ``conv`` and
   ``softcap``) beside ``right`` (``heads``, ``dim``, ``vdim``, ``tau``; the rank of its decay projection is read off the
   checkpoint's shapes by the weight plan and may be given as ``rank``).
 
@@ -65,14 +65,15 @@ class ConvWindowAttentionSizes:
     dim: int
     vdim: int
     scale: float
-    window: int
-    conv: int = 1                           # taps; 1: no convolution
+    window: Optional[int]                   # None: every earlier key
+    conv: Optional[int] = None              # taps (one tap: a factor per channel); None: no convolution, no such tensors
     softcap: Optional[float] = None
 
     def to_json(self):
-        out: Dict[str, Any] = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "mask": {"size": self.window},
-                               "scale": self.scale, "vdim": self.vdim}
-        if self.conv > 1:
+        out: Dict[str, Any] = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "scale": self.scale, "vdim": self.vdim}
+        if self.window is not None:
+            out["mask"] = {"size": self.window}
+        if self.conv is not None:
             out["conv"] = self.conv
         if self.softcap is not None:
             out["softcap"] = self.softcap
@@ -143,8 +144,8 @@ def _rotary_attention(m: Dict[str, Any], what: str) -> RotaryAttentionSizes:
 
 def _conv_window_attention(m: Dict[str, Any], what: str) -> ConvWindowAttentionSizes:
     heads, kv_heads, dim, vdim = _heads(m, what)
-    window = _int(_obj(m.get("mask"), what + ".mask"), "size", what + ".mask")
-    conv = 1 if m.get("conv") is None else _int(m, "conv", what)
+    window = None if m.get("mask") is None else _int(_obj(m["mask"], what + ".mask"), "size", what + ".mask")
+    conv = None if m.get("conv") is None else _int(m, "conv", what)
     softcap = None
     if m.get("softcap") is not None:
         softcap = _num(m, "softcap", what)

@@ -39,10 +39,10 @@ class AttentionMixer:
 
     ``qk_norm_wide`` (with ``qk_norm_eps``): the norm runs over the whole query projection at once (all heads' values
     together, ``q_norm`` [H * hd]) and over the whole key projection (``k_norm`` [Hkv * hd]) instead of head by head.
-    ``conv_taps`` n > 1: every channel of the [q; k; v] projection passes a causal convolution over the request's last n
+    ``conv_taps`` n: every channel of the [q; k; v] projection passes a causal convolution over the request's last n
     tokens before anything else (``conv`` [channels, n], column n-1 weighs the newest token; no bias, no activation;
-    nothing before the first token); the request's last n-1 projected rows are state, kept in its state slot from
-    ``state_offset`` on."""
+    nothing before the first token; one tap is a factor per channel); the request's last n-1 projected rows are state, kept
+    in its state slot from ``state_offset`` on."""
 
     graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
 
@@ -72,7 +72,7 @@ class AttentionMixer:
         if self.softcap is not None and not self.softcap > 0:
             raise ValueError("attention: the soft cap of the scores must be positive")
         self.wide_norm = bool(params.get("qk_norm_wide", False))
-        self.conv_taps = int(params.get("conv_taps") or 1)
+        self.conv_taps = int(params["conv_taps"]) if params.get("conv_taps") else None
         self.state_offset = 0
         slopes = params.get("distance_slopes")
         if slopes is not None and len(slopes) != self.num_heads:
@@ -86,7 +86,7 @@ class AttentionMixer:
         self.out_scale = float(params.get("out_scale", 1.0))
         on_device = getattr(self.position, "freq", None) is not None
         self.extended = (self.values_are_keys or self.qk_norm_eps is not None or self.sink or self.head_gate
-                         or self.out_scale != 1.0 or on_device or self.row_form or self.conv_taps > 1)
+                         or self.out_scale != 1.0 or on_device or self.row_form or self.conv_taps is not None)
         if self.row_form:
             if self.head_gate or self.out_scale != 1.0 or self.values_are_keys:
                 raise ValueError("attention: a gate, an output factor or values taken from the keys cannot be combined with "
@@ -128,7 +128,7 @@ class AttentionMixer:
         if tuple(weights["w_o"].shape) != (self.hidden_size, self.num_heads * self.value_dim):
             raise ValueError(f"attention: w_o has shape {tuple(weights['w_o'].shape)}")
         self.conv = None
-        if self.conv_taps > 1:
+        if self.conv_taps is not None:
             if self.head_gate or self.values_are_keys:
                 raise ValueError("attention: a convolution of the projections cannot be combined with a head gate or values taken from the keys")
             if not (self.conv_taps <= 17):
@@ -169,7 +169,7 @@ class AttentionMixer:
                          value_dim=None if self.value_dim == self.head_dim else self.value_dim, chunk=self.chunk)
 
     def state_need(self):
-        if self.conv is None:
+        if self.conv is None or self.conv_taps == 1:
             return None
         return StateNeed(((self.conv_taps - 1) * self.conv_channels,), "float32")
 
@@ -271,7 +271,8 @@ class AttentionMixer:
         self.w_qkv.forward(xn, proj)
         if self.conv is not None:
             mixed = ctx.scratch("att_proj_conv", (T, self.conv_channels), torch.float32)
-            kernels.causal_conv(proj, 0, self.conv, None, ctx.state(run.cache_layer), self.state_offset, ctx.row_req,
+            state = ctx.state(run.cache_layer) if self.conv_taps > 1 else mixed      # one tap reaches no earlier token: no state is touched
+            kernels.causal_conv(proj, 0, self.conv, None, state, self.state_offset if self.conv_taps > 1 else 0, ctx.row_req,
                                 ctx.seg_start, ctx.seg_len, ctx.state_slots, mixed, activate=False)
             proj = mixed
         k_off = H * hd

@@ -309,7 +309,7 @@ def fovezen_weight_plan(cfg) -> WeightPlan:
             q = p + "mix.left."
             for name, rows in (("q", a.heads * a.dim), ("k", a.kv_heads * a.dim), ("v", a.kv_heads * a.vdim)):
                 rules.append(TensorRule(q + name, (rows, D)))
-                if a.conv > 1:
+                if a.conv is not None:
                     rules.append(TensorRule(q + name + ".conv", (rows, a.conv), "vector", (0.0, 0.5)))
             rules += [TensorRule(q + "q.norm", (a.dim,), "vector"), TensorRule(q + "k.norm", (a.dim,), "vector"),
                       TensorRule(q + "o", (D, a.heads * a.vdim))]
@@ -345,7 +345,7 @@ def fovezen_weight_plan(cfg) -> WeightPlan:
             else:
                 a, b = p + "mix.left.", q + "mixer.left."
                 out[b + "w_qkv"] = _cat([t[a + "q"], t[a + "k"], t[a + "v"]])
-                if layer.mixer.left.conv > 1:
+                if layer.mixer.left.conv is not None:
                     out[b + "conv"] = _cat([t[a + "q.conv"], t[a + "k.conv"], t[a + "v.conv"]])
                 out[b + "q_norm"], out[b + "k_norm"], out[b + "w_o"] = t[a + "q.norm"], t[a + "k.norm"], t[a + "o"]
                 a, b = p + "mix.right.", q + "mixer.right."

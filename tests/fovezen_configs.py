@@ -33,7 +33,9 @@ def mamba2(heads, vdim, state, groups, conv, norm_groups, ff=None, limit=1.0):
 
 
 def left(heads, kv_heads, dim, vdim, scale, window, conv=None, softcap=None):
-    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": window}}
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if window is not None:
+        m["mask"] = {"size": window}
     if conv is not None:
         m["conv"] = conv
     if softcap is not None:
@@ -77,19 +79,21 @@ FOV_B = model(128, 300, 1e-6, [
     attention(2, 1, 64, 64, 0.2, ff=96, limit=3.0),
 ], streams=4, loop=(1, 4, 2))
 
-# C: one copy of the stream (with its own weights), no loop, a window shorter than a page and one longer than every prompt
+# C: one copy of the stream (with its own weights), no loop, a window shorter than a page and one longer than every prompt,
+# a convolution of one tap (a factor per channel, no state)
 FOV_C = model(80, 170, 1e-5, [
     parallel(left(5, 5, 16, 16, 0.25, 5, conv=3, softcap=50.0), right(5, 16, 16, 1.0, 24), ff=100, limit=1.0),
     attention(2, 1, 48, 16, 0.15, rot=rot(20.0, 48, (2.0, 1.0, 8.0, 16))),
-    parallel(left(2, 2, 48, 80, 0.15, 400), right(1, 64, 80, 30.0, 8), ff=40, limit=4.0),
+    parallel(left(2, 2, 48, 80, 0.15, 400, conv=1), right(1, 64, 80, 30.0, 8), ff=40, limit=4.0),
     mamba2(1, 80, 64, 1, 1, 1, ff=60, limit=1.2),
 ], streams=1, logit_scale=2.0)
 
-# D: no copies at all (a plain residual stream), a loop of one layer run four times, a width that is no multiple of 8
+# D: no copies at all (a plain residual stream), a loop of one layer run four times, a width that is no multiple of 8,
+# a parallel pair whose attention has no window
 FOV_D = model(100, 77, 1e-3, [
     attention(3, 3, 32, 32, 0.18, rot=rot(300.0, 16)),
     mamba2(2, 40, 48, 2, 2, 1, ff=56, limit=0.9),
-    parallel(left(3, 1, 32, 16, 0.3, 33, conv=2), right(2, 32, 48, 4.0, 16), ff=88, limit=1.1),
+    parallel(left(3, 1, 32, 16, 0.3, None, conv=2), right(2, 32, 48, 4.0, 16), ff=88, limit=1.1),
 ], loop=(1, 2, 4))
 
 SHARP = {"std": 0.12}

@@ -130,7 +130,7 @@ def window_conv_attention(W, p, m, h, eps, dt, rnd):
         q, k, v = (short_conv(u, W[p + n + ".conv"]) for u, n in ((q, "q"), (k, "k"), (v, "v")))
     q = norm_plain(q.reshape(T, H, d), W[p + "q.norm"], eps)
     k = norm_plain(k.reshape(T, G, d), W[p + "k.norm"], eps)
-    o = softmax_attention(q, k, v.reshape(T, G, dv), m["scale"], rnd, window=m["mask"]["size"], softcap=m.get("softcap"))
+    o = softmax_attention(q, k, v.reshape(T, G, dv), m["scale"], rnd, window=(m.get("mask") or {}).get("size"), softcap=m.get("softcap"))
     return linear(W[p + "o"], o.reshape(T, H * dv), rnd)
 
 

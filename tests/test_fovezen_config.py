@@ -57,7 +57,7 @@ def test_every_constant_is_read_from_the_file():
 
 @pytest.mark.parametrize("change, message", [
     (lambda c: c["layers"][0].update(type="lightning"), "unknown type"),
-    (lambda c: c["layers"][1]["mixer"]["left"].pop("mask"), "mask"),
+    (lambda c: c["layers"][1]["mixer"]["left"].update(mask={}), "mask"),
     (lambda c: c["layers"][1]["mixer"]["right"].update(tau=0), "tau"),
     (lambda c: c["layers"][2]["mixer"]["rot"].update(dims=18), "dims"),
     (lambda c: c["layers"][2]["mixer"].update(kv_heads=4), "multiple"),

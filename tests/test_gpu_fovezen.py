@@ -322,7 +322,7 @@ def _left_part(D, m, w, dtype, p="p."):
     if m.get("conv"):
         weights["conv"] = torch.cat([w[p + "q.conv"], w[p + "k.conv"], w[p + "v.conv"]])
     return MIXERS["attention"]({"hidden_size": D, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
-                                "value_dim": m["vdim"], "scale": m["scale"], "window": m["mask"]["size"], "position": PartSpec("none", {}),
+                                "value_dim": m["vdim"], "scale": m["scale"], "window": (m.get("mask") or {}).get("size"), "position": PartSpec("none", {}),
                                 "qk_norm_eps": EPS, "conv_taps": m.get("conv"), "softcap": m.get("softcap")}, weights, _build(dtype))
 
 
@@ -335,6 +335,7 @@ def _left_ctx(part, m, dtype, n, max_len=256, page_size=8):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m", [LEFT, dict(LEFT, heads=2, kv_heads=2, dim=64, vdim=64, conv=2, softcap=None, mask={"size": 5}),
                                dict(LEFT, heads=4, kv_heads=1, dim=32, vdim=16, conv=None, mask={"size": 300}),
+                               dict(LEFT, heads=3, kv_heads=3, dim=16, vdim=32, conv=1, mask=None),
                                # soft-capped scores at the head sizes whose prompt portions the tcgen05 kernel runs
                                dict(LEFT, heads=4, kv_heads=2, dim=64, vdim=64, conv=2, softcap=2.5, scale=0.5, mask={"size": 23}),
                                dict(LEFT, heads=2, kv_heads=1, dim=128, vdim=128, conv=None, softcap=1.5, scale=0.3, mask={"size": 300})])
@@ -344,7 +345,7 @@ def test_window_attention_with_a_convolution_of_its_projections(dtype, m, cut):
     g = torch.Generator().manual_seed(9)
     w = _left_weights(D, m, g)
     part = _left_part(D, m, w, dtype)
-    if m.get("conv"):
+    if (m.get("conv") or 1) > 1:
         assert part.state_need().shape == ((m["conv"] - 1) * ((m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"]),)
     else:
         assert part.state_need() is None
@@ -627,18 +628,20 @@ def _plain(case, folder, rounded=False, single=False):
     return _PLAIN[key]
 
 
-def _bound(exact, other, floor):
-    """Three times the distance between the plain model in two precisions, and at least ``floor``."""
-    return max(floor, 3.0 * max(tt.rel_err(other[r], exact[r]) for r in exact))
+def _bound(exact, other, floor, times=3.0):
+    """``times`` the distance between the plain model in two precisions, and at least ``floor``."""
+    return max(floor, times * max(tt.rel_err(other[r], exact[r]) for r in exact))
 
 
 def _tolerance(case, folder, dtype):
-    """Three times the distance between the exact plain model and the plain model computed in the engine's precision
-    (32-bit throughout, or with bfloat16 operands of the matrix products): the engine rounds at the same places, its sums
-    run in other orders. A norm that follows a nearly cancelling sum (a query and a key at right angles at a sequence's
-    first token) can raise a position's 32-bit rounding far above 1e-5 in any 32-bit implementation, the plain one included."""
+    """bfloat16: three times the distance between the exact plain model and the plain model with bfloat16 operands of the
+    matrix products: the engine rounds at the same places, its sums run in other orders. 32-bit: 3e-5, or eight times the
+    distance between the plain model in float64 and in float32 where that is more: a norm that follows a nearly cancelling sum
+    (a query and a key at right angles at a sequence's first tokens, whose product is all that a head's memory holds yet)
+    raises a position's 32-bit rounding far above 1e-5 in any 32-bit implementation, the plain one included, by a factor that
+    depends on the order of its sums. (A wrong key, window, state or copy moves these models' logits by a tenth of their size.)"""
     if dtype == "float32":
-        return _bound(_plain(case, folder), _plain(case, folder, single=True), 3e-5)
+        return _bound(_plain(case, folder), _plain(case, folder, single=True), 3e-5, 8.0)
     return _bound(_plain(case, folder), _plain(case, folder, True), 0.0)
 
 
@@ -820,7 +823,7 @@ def _random_config(seed):
             kv = r.choice([1, 2, 4])
             dim = r.choice([16, 24, 32, 64, 80, 128])
             layers.append(fc.parallel(fc.left(kv * r.choice([1, 2, 3]), kv, dim, r.choice([dim, 16, 48, 96]), r.choice([0.1, 0.125, 0.3]),
-                                              r.choice([3, 16, 17, 50, 96, 1000]), conv=r.choice([None, 2, 3, 4]), softcap=r.choice([None, 5.0, 30.0])),
+                                              r.choice([None, 1, 3, 16, 17, 50, 96, 1000]), conv=r.choice([None, 1, 2, 3, 4]), softcap=r.choice([None, 5.0, 30.0])),
                                       fc.right(r.randint(1, 6), r.choice([8, 16, 32, 48, 72, 128]), r.choice([8, 16, 32, 40, 96]), r.choice([1.0, 4.0, 16.0]),
                                                r.choice([4, 8, 16, 20, 32])), ff=f, limit=limit))
     n = len(layers)
@@ -843,7 +846,7 @@ def test_random_configurations_under_a_mixed_trace(seed, tmp_path):
     single = {rid: pf.forward(w, cfg, toks, torch.float32).double().numpy() for rid, toks in reqs.items()}
     steps = tt.trace_mixed(reqs, seed=seed, tail=10)
     for dtype in ("float32", "bfloat16"):
-        tol = _bound(exact, single, 3e-5) if dtype == "float32" else _bound(exact, rounded, 0.0)
+        tol = _bound(exact, single, 3e-5, 8.0) if dtype == "float32" else _bound(exact, rounded, 0.0)
         engine = _engine(folder, dtype, tt.max_tokens_of(steps, reqs, 16) // 16 + 4)
         got = tt.run_in_process(engine, steps)
         engine.check_status()
