@@ -322,7 +322,14 @@ class ParallelMixer:
                 return None
             key += tuple(k)
         if self.combine == "mean_normed":
-            key += (self._sums_clear(ctx, self._sums(ctx, ctx.n_tokens)),)
+            # decided here, once per run and before it: a run that is repeated from its launch program does not pass through
+            # ``forward``, and the next mixer of this kind must still learn that the sums are zero after this one
+            sums = self._sums(ctx, ctx.n_tokens)
+            clear = self._sums_clear(ctx, sums)
+            if getattr(ctx, "carry", None) is not None:
+                ctx.carry["parallel_branch_decided"] = (id(self), run.cache_layer, clear)
+                ctx.carry["parallel_branch_sums"] = tuple(t.data_ptr() for t in sums)
+            key += (clear,)
         return key
 
     takes_then = True
@@ -340,14 +347,18 @@ class ParallelMixer:
         if self.combine == "mean_normed":
             # every branch adds into a sum of its own, which the combining kernel norms, adds to x and clears again
             sums = self._sums(ctx, xn.shape[0])
-            clear = self._sums_clear(ctx, sums)
+            carry = getattr(ctx, "carry", None)
+            decided = carry.get("parallel_branch_decided") if carry is not None else None
+            if decided is not None and decided[:2] == (id(self), run.cache_layer):
+                clear = decided[2]                       # ``launch_key`` looked before it marked the sums as zero
+            else:
+                clear = self._sums_clear(ctx, sums)
             for (_, m), own in zip(self.branches, sums):
                 if not clear:
                     kernels.scale_cast(x, own, None, 0.0)
                 m.forward(ctx, run, xn, own)
             for own, w in zip(sums, self.out_norms):
                 kernels.add_normed(own, w, x, self.eps, clear_y=True)
-            carry = getattr(ctx, "carry", None)
             if carry is not None:
                 carry["parallel_branch_sums"] = tuple(t.data_ptr() for t in sums)
             return
